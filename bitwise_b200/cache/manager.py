@@ -351,10 +351,10 @@ class CacheManager:
 def groups_from_needs(needs: Sequence[object]) -> List[GroupSpec]:
     """Group cache entries by what must be kept: entries with paged keys and the same
     window share a group (and so a block table); entries without paged keys form none."""
-    from ..parts.base import PagedKVNeed
+    from ..parts.base import PagedKVNeed, PagedLatentNeed
     by_window: Dict[Optional[int], List[int]] = {}
     for e, need in enumerate(needs):
-        if isinstance(need, PagedKVNeed):
+        if isinstance(need, (PagedKVNeed, PagedLatentNeed)):
             by_window.setdefault(need.window, []).append(e)
     keys = sorted(by_window, key=lambda w: (w is not None, w or 0))
     return [GroupSpec(w, tuple(by_window[w])) for w in keys]

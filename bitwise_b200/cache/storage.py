@@ -2,7 +2,8 @@
 
 Per cache entry (layer run) keys and values are ``[pages, kv_heads, page_size,
 head_dim]`` each, the reference's layout per layer (src/kernels.h:91-103;
-src/model.cpp:241-248), in the dtype of the path.  A page id indexes every entry of its
+src/model.cpp:241-248), in the dtype of the path; an entry of a latent-attention layer is one
+tensor ``[pages, page_size, rank + rot_dim]``.  A page id indexes every entry of its
 group at once, as the reference's block id indexes every layer (src/model.h:69-70).
 Slot state is ``[slots, *shape]`` per entry that asks for it, plus one 64-bit word per
 slot for the request's logits fingerprint.  Nothing is zeroed on reuse: reads are limited
@@ -18,7 +19,7 @@ from typing import List, Optional, Sequence
 
 import torch
 
-from ..parts.base import PagedKVNeed, PagedKVView, SlotStateNeed, SlotStateView
+from ..parts.base import PagedKVNeed, PagedKVView, PagedLatentNeed, PagedLatentView, SlotStateNeed, SlotStateView
 from .manager import CacheManager, GroupSpec
 
 FINGERPRINT_SEED = 1469598103934665603  # src/engine.h:68
@@ -43,6 +44,10 @@ class CacheStorage:
                 shape = (max(pages, 1) + 1, need.kv_heads, page_size, need.head_dim)
                 self.k[e] = torch.zeros(shape, dtype=dtype, device=device)
                 self.v[e] = torch.zeros(shape, dtype=dtype, device=device)
+            elif isinstance(need, PagedLatentNeed):
+                # one tensor holds the latent and the shared rotated key part of a position
+                pages = pages_per_group[self.group_of_entry[e]]
+                self.k[e] = torch.zeros((max(pages, 1) + 1, page_size, need.rank + need.rot_dim), dtype=dtype, device=device)
             elif isinstance(need, SlotStateNeed):
                 self.state[e] = torch.zeros((max(num_slots, 1) + 1,) + tuple(need.shape), dtype=need.dtype, device=device)
             elif need is not None:
@@ -61,6 +66,8 @@ class CacheStorage:
         for e, need in enumerate(self.needs):
             if isinstance(need, PagedKVNeed):
                 out.append(PagedKVView(self.k[e], self.v[e], block_tables[self.group_of_entry[e]], self.page_size))
+            elif isinstance(need, PagedLatentNeed):
+                out.append(PagedLatentView(self.k[e], block_tables[self.group_of_entry[e]], self.page_size))
             elif isinstance(need, SlotStateNeed):
                 out.append(SlotStateView(self.state[e], seq_slot))
             else:

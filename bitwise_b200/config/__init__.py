@@ -1,8 +1,10 @@
 from .base import ConfigError, read_config_json
 from .llama import LlamaConfig, RopeScaling
+from .nuderax import LatentMixerConfig, NuderaxConfig, NuderaxLayerConfig, RoutedMlpConfig
 from .registry import (Architecture, architecture_of, config_from_folder, known_architectures,
                        lookup_architecture, register_architecture)
 
-__all__ = ["ConfigError", "LlamaConfig", "RopeScaling", "read_config_json", "Architecture",
+__all__ = ["ConfigError", "LlamaConfig", "RopeScaling", "NuderaxConfig", "NuderaxLayerConfig", "LatentMixerConfig",
+           "RoutedMlpConfig", "read_config_json", "Architecture",
            "architecture_of", "config_from_folder", "known_architectures", "lookup_architecture",
            "register_architecture"]

@@ -46,6 +46,8 @@ def lookup_architecture(name: str) -> Architecture:
 
 def architecture_of(config_json: dict) -> Architecture:
     archs = config_json.get("architectures")
+    if not archs and isinstance(config_json.get("architecture"), str):
+        archs = [config_json["architecture"]]  # some designs name theirs in one string
     if not archs:
         raise ConfigError("config.json has no 'architectures' entry")
     return lookup_architecture(archs[0])
@@ -61,3 +63,5 @@ def config_from_folder(folder: str):
 def _ensure_builtin() -> None:
     if "LlamaForCausalLM" not in _ARCHITECTURES:
         from ..models import llama  # noqa: F401  (registers itself on import)
+    if "Nuderax" not in _ARCHITECTURES:
+        from ..models import nuderax  # noqa: F401

@@ -1,0 +1,411 @@
+// Attention over a latent cache. A token keeps one vector of `rank` + `rot_dim` numbers for all
+// heads: a normed latent c, from which every head's keys and values are linear maps, and one
+// rotated key part that the heads share. With the heads' key maps folded into the queries
+// (q' = W_uk^T q, done by the caller as a product per head) a head's score against a cached
+// token is one dot product of rank + rot_dim terms against that vector, and what attention
+// returns per head is the weighted sum of latents, which the caller maps to values afterwards:
+// the cache is read once for all heads and never expanded.
+//
+// Kernels: the store (root-mean-square norm of the latent, rotation of the shared key part,
+// write into the page), the rotation of the queries' rotated parts, attention for query tiles
+// (prompt portions and steps of few rows alike), and attention split over the keys for steps of
+// single rows, with its merge. Scores, softmax weights, sums and rotations are float32 in both
+// precisions.
+#include "bw_act.cuh"
+
+#include <math.h>
+
+namespace {
+
+// ---------------------------------------------------------------------------------------
+// The rotation of pair i (entries 2i and 2i + 1 of a vector) by the table row of the
+// position: (u, v) -> (u cos - v sin, v cos + u sin). `pairs` pairs are turned, entries
+// from 2 * pairs on pass unchanged.
+__device__ __forceinline__ void turn(float u, float v, float c, float s, float& ru, float& rv) {
+  ru = __fsub_rn(__fmul_rn(u, c), __fmul_rn(v, s));
+  rv = __fadd_rn(__fmul_rn(v, c), __fmul_rn(u, s));
+}
+
+// One block per row: d = the row of the down projection (float32, rank + rot_dim wide).
+// cache[page][slot] = [ d[:rank] / sqrt(mean(d[:rank]^2) + eps) * w | turn(d[rank:]) ].
+__global__ void __launch_bounds__(128)
+latent_store_kernel(const float* __restrict__ d, int d_stride, const float* __restrict__ w, float eps,
+                    const int* __restrict__ pos, const int* __restrict__ row_seq, const float* __restrict__ cos_t,
+                    const float* __restrict__ sin_t, int pairs, const int* __restrict__ block_table, int max_blocks,
+                    act_t* cache, int rank, int rot_dim, int page) {
+  bw::pdl_enter();
+  __shared__ float red[32];
+  const int r = blockIdx.x;
+  const float* dr = d + static_cast<size_t>(r) * d_stride;
+  const int p = pos[r];
+  const int blk = block_table[static_cast<size_t>(row_seq[r]) * max_blocks + p / page];
+  act_t* dst = cache + (static_cast<size_t>(blk) * page + p % page) * (rank + rot_dim);
+  float ss = 0.0f;
+  for (int i = threadIdx.x; i < rank; i += blockDim.x) ss = __fmaf_rn(dr[i], dr[i], ss);
+  const float inv = bw::rms_scale(bw::block_sum(ss, red), rank, eps);
+  for (int i = threadIdx.x; i < rank; i += blockDim.x) dst[i] = bw::from_f<act_t>(bw::rms_apply(dr[i], inv, w[i]));
+  const float* kr = dr + rank;
+  for (int i = threadIdx.x; i < (rot_dim + 1) / 2; i += blockDim.x) {
+    const float u = kr[2 * i];
+    if (2 * i + 1 >= rot_dim) {  // an odd last entry has no partner
+      dst[rank + 2 * i] = bw::from_f<act_t>(u);
+      continue;
+    }
+    const float v = kr[2 * i + 1];
+    float ru = u, rv = v;
+    if (i < pairs) turn(u, v, cos_t[static_cast<size_t>(p) * pairs + i], sin_t[static_cast<size_t>(p) * pairs + i], ru, rv);
+    dst[rank + 2 * i] = bw::from_f<act_t>(ru);
+    dst[rank + 2 * i + 1] = bw::from_f<act_t>(rv);
+  }
+}
+
+// The rotated part of every head's query: `rot_dim` entries at q[row][h * head_stride + offset],
+// turned and written to out[row][h * out_head_stride + out_offset]. Grid: (row, head).
+__global__ void __launch_bounds__(64)
+rotate_heads_kernel(const act_t* __restrict__ q, int q_stride, int head_stride, int offset, act_t* out, int o_stride,
+                    int out_head_stride, int out_offset, int rot_dim, int pairs, const int* __restrict__ pos,
+                    const float* __restrict__ cos_t, const float* __restrict__ sin_t) {
+  bw::pdl_enter();
+  const int r = blockIdx.x, h = blockIdx.y;
+  const int p = pos[r];
+  const act_t* src = q + static_cast<size_t>(r) * q_stride + h * head_stride + offset;
+  act_t* dst = out + static_cast<size_t>(r) * o_stride + h * out_head_stride + out_offset;
+  for (int i = threadIdx.x; i < (rot_dim + 1) / 2; i += blockDim.x) {
+    const float u = bw::to_f(src[2 * i]);
+    if (2 * i + 1 >= rot_dim) {
+      dst[2 * i] = bw::from_f<act_t>(u);
+      continue;
+    }
+    const float v = bw::to_f(src[2 * i + 1]);
+    float ru = u, rv = v;
+    if (i < pairs) turn(u, v, cos_t[static_cast<size_t>(p) * pairs + i], sin_t[static_cast<size_t>(p) * pairs + i], ru, rv);
+    dst[2 * i] = bw::from_f<act_t>(ru);
+    dst[2 * i + 1] = bw::from_f<act_t>(rv);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Attention. Keys are walked in tiles of 32 at fixed absolute positions (tile t holds positions
+// 32 t .. 32 t + 31); lane l of a warp owns key l of the tile. A warp works on one query (a row
+// and a head) at a time: the score of its key, the tile's maximum and sum over the warp, and
+// the running (maximum, sum, weighted sum of latents) of the query, rescaled tile by tile. What
+// a query gets depends on its own keys and on the fixed tiles only: not on the other queries of
+// the block, nor on where the block started. A tile in which a query sees no key leaves its
+// state untouched.
+constexpr int kWarps = 8;
+constexpr int kKeys = 32;
+constexpr int kThreads = kWarps * 32;
+
+struct QueryState {
+  float m, l;
+};
+
+// One tile of keys in shared memory (`keys`, rows of `ks` floats) against the query `qv`
+// (`dk` floats in shared memory) of position `pq`: updates m, l and acc (entry i of acc is
+// latent dimension 32 i + lane).
+template <int ACC>
+__device__ __forceinline__ void attend_tile(const float* keys, int ks, const float* qv, int dk, int rank, int k0,
+                                            int lo, int pq, float scale, int lane, float& m, float& l, float* acc) {
+  const int kp = k0 + lane;
+  const float* kv = keys + lane * ks;
+  float s = 0.0f;
+  for (int d = 0; d < dk; ++d) s = __fmaf_rn(qv[d], kv[d], s);
+  s = __fmul_rn(s, scale);
+  const bool seen = kp <= pq && kp >= lo;
+  if (!seen) s = -INFINITY;
+  const float mt = bw::warp_max(s);
+  if (mt == -INFINITY) return;  // the same for all lanes
+  const float mn = fmaxf(m, mt);
+  const float alpha = m == -INFINITY ? 0.0f : expf(__fsub_rn(m, mn));
+  const float p = seen ? expf(__fsub_rn(s, mn)) : 0.0f;
+  l = __fmaf_rn(l, alpha, bw::warp_sum(p));
+#pragma unroll
+  for (int i = 0; i < ACC; ++i) acc[i] = __fmul_rn(acc[i], alpha);
+  for (int kk = 0; kk < kKeys; ++kk) {
+    const float pk = __shfl_sync(0xffffffffu, p, kk);
+    if (pk == 0.0f) continue;
+    const float* vrow = keys + kk * ks;
+#pragma unroll
+    for (int i = 0; i < ACC; ++i) {
+      const int d = i * 32 + lane;
+      if (d < rank) acc[i] = __fmaf_rn(pk, vrow[d], acc[i]);
+    }
+  }
+  m = mn;
+}
+
+// Loads the keys k0 .. k0 + 31 of one sequence (those up to `last`) into shared memory.
+__device__ __forceinline__ void load_keys(float* keys, int ks, const act_t* __restrict__ cache, const int* __restrict__ bt,
+                                          int page, int dk, int k0, int last, int warp, int lane) {
+  for (int kk = warp; kk < kKeys; kk += kWarps) {
+    const int kp = k0 + kk;
+    float* dst = keys + kk * ks;
+    if (kp <= last) {
+      const act_t* src = cache + (static_cast<size_t>(bt[kp / page]) * page + kp % page) * dk;
+      for (int d = lane; d < dk; d += 32) dst[d] = bw::to_f(src[d]);
+    } else {
+      for (int d = lane; d < dk; d += 32) dst[d] = 0.0f;
+    }
+  }
+}
+
+// Query tiles: a block takes the rows of one tile (rows of one sequence, consecutive positions)
+// and `hb` heads from h0 = blockIdx.y * hb on; its queries are (row, head) pairs, at most
+// kWarps * QW of them, query i on warp i % kWarps.
+template <int ACC, int QW>
+__global__ void __launch_bounds__(kThreads)
+latent_attention_kernel(const act_t* __restrict__ q, int q_stride, const act_t* __restrict__ cache,
+                        const int* __restrict__ block_table, int max_blocks, const int* __restrict__ tile_seq,
+                        const int* __restrict__ tile_row0, const int* __restrict__ tile_rows,
+                        const int* __restrict__ seq_pos0, const int* __restrict__ seq_row0, act_t* out, int o_stride,
+                        int heads, int hb, int rank, int rot_dim, int page, int window, float scale) {
+  bw::pdl_enter();
+  extern __shared__ float sm[];
+  const int dk = rank + rot_dim, ks = dk + 1;
+  float* keys = sm;
+  float* qs = sm + kKeys * ks;
+  const int t = blockIdx.x;
+  const int seq = tile_seq[t], row0 = tile_row0[t], rows = tile_rows[t];
+  const int h0 = blockIdx.y * hb;
+  const int nh = min(hb, heads - h0);
+  const int nq = rows * nh;
+  const int p0 = seq_pos0[seq] + (row0 - seq_row0[seq]);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int qi = warp; qi < nq; qi += kWarps) {
+    const act_t* src = q + static_cast<size_t>(row0 + qi / nh) * q_stride + (h0 + qi % nh) * dk;
+    for (int d = lane; d < dk; d += 32) qs[qi * dk + d] = bw::to_f(src[d]);
+  }
+  float m[QW], l[QW], acc[QW][ACC];
+#pragma unroll
+  for (int j = 0; j < QW; ++j) {
+    m[j] = -INFINITY, l[j] = 0.0f;
+#pragma unroll
+    for (int i = 0; i < ACC; ++i) acc[j][i] = 0.0f;
+  }
+  const int last = p0 + rows - 1;
+  const int first = window > 0 ? max(0, p0 - window + 1) : 0;
+  const int* bt = block_table + static_cast<size_t>(seq) * max_blocks;
+  for (int k0 = first / kKeys * kKeys; k0 <= last; k0 += kKeys) {
+    __syncthreads();
+    load_keys(keys, ks, cache, bt, page, dk, k0, last, warp, lane);
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < QW; ++j) {
+      const int qi = warp + kWarps * j;
+      if (qi >= nq) continue;
+      const int pq = p0 + qi / nh;
+      const int lo = window > 0 ? max(0, pq - window + 1) : 0;
+      attend_tile<ACC>(keys, ks, qs + qi * dk, dk, rank, k0, lo, pq, scale, lane, m[j], l[j], acc[j]);
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < QW; ++j) {
+    const int qi = warp + kWarps * j;
+    if (qi >= nq) continue;
+    act_t* dst = out + static_cast<size_t>(row0 + qi / nh) * o_stride + (h0 + qi % nh) * rank;
+    const float inv = __fdiv_rn(1.0f, l[j]);
+#pragma unroll
+    for (int i = 0; i < ACC; ++i) {
+      const int d = i * 32 + lane;
+      if (d < rank) dst[d] = bw::from_f<act_t>(__fmul_rn(acc[j][i], inv));
+    }
+  }
+}
+
+// Steps of single rows: the keys of a row are cut into spans of `span` keys (a multiple of 32,
+// at fixed absolute positions); a block takes one span of one row and up to kWarps heads, walks
+// the span's tiles as above, and leaves (m, l, weighted sum) per head and span. The merge folds
+// a query's spans in ascending order.
+template <int ACC>
+__global__ void __launch_bounds__(kThreads)
+latent_attention_split_kernel(const act_t* __restrict__ q, int q_stride, const act_t* __restrict__ cache,
+                              const int* __restrict__ block_table, int max_blocks, const int* __restrict__ row_seq,
+                              const int* __restrict__ pos, float* __restrict__ part, int spans, int span, int heads,
+                              int rank, int rot_dim, int page, int window, float scale) {
+  bw::pdl_enter();
+  extern __shared__ float sm[];
+  const int dk = rank + rot_dim, ks = dk + 1;
+  float* keys = sm;
+  float* qs = sm + kKeys * ks;
+  const int r = blockIdx.x, sp = blockIdx.y, h0 = blockIdx.z * kWarps;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = h0 + warp;
+  const int pq = pos[r];
+  const int lo = window > 0 ? max(0, pq - window + 1) : 0;
+  const int begin = max(sp * span, lo / kKeys * kKeys), end = min(pq, (sp + 1) * span - 1);
+  float* rec = part + ((static_cast<size_t>(r) * heads + h) * spans + sp) * (rank + 2);
+  if (begin > end) {  // nothing of this span is seen
+    if (h < heads && lane == 0) rec[0] = -INFINITY, rec[1] = 0.0f;
+    return;
+  }
+  if (h < heads) {
+    const act_t* src = q + static_cast<size_t>(r) * q_stride + h * dk;
+    for (int d = lane; d < dk; d += 32) qs[warp * dk + d] = bw::to_f(src[d]);
+  }
+  float m = -INFINITY, l = 0.0f, acc[ACC];
+#pragma unroll
+  for (int i = 0; i < ACC; ++i) acc[i] = 0.0f;
+  const int* bt = block_table + static_cast<size_t>(row_seq[r]) * max_blocks;
+  for (int k0 = begin; k0 <= end; k0 += kKeys) {
+    __syncthreads();
+    load_keys(keys, ks, cache, bt, page, dk, k0, end, warp, lane);
+    __syncthreads();
+    if (h < heads) attend_tile<ACC>(keys, ks, qs + warp * dk, dk, rank, k0, lo, pq, scale, lane, m, l, acc);
+  }
+  if (h >= heads) return;
+  if (lane == 0) rec[0] = m, rec[1] = l;
+#pragma unroll
+  for (int i = 0; i < ACC; ++i) {
+    const int d = i * 32 + lane;
+    if (d < rank) rec[2 + d] = acc[i];
+  }
+}
+
+// One block per (row, head): folds the spans' records in ascending order.
+__global__ void __launch_bounds__(128)
+latent_attention_merge_kernel(const float* __restrict__ part, const int* __restrict__ pos, int spans, int span,
+                              int heads, int rank, act_t* out, int o_stride) {
+  bw::pdl_enter();
+  const int r = blockIdx.x, h = blockIdx.y;
+  const float* rec0 = part + (static_cast<size_t>(r) * heads + h) * spans * (rank + 2);
+  const int used = min(spans, pos[r] / span + 1);
+  float m = -INFINITY;
+  for (int s = 0; s < used; ++s) m = fmaxf(m, rec0[static_cast<size_t>(s) * (rank + 2)]);
+  float l = 0.0f;
+  for (int s = 0; s < used; ++s) {
+    const float* rec = rec0 + static_cast<size_t>(s) * (rank + 2);
+    if (rec[0] != -INFINITY) l = __fmaf_rn(rec[1], expf(__fsub_rn(rec[0], m)), l);
+  }
+  const float inv = __fdiv_rn(1.0f, l);
+  for (int d = threadIdx.x; d < rank; d += blockDim.x) {
+    float a = 0.0f;
+    for (int s = 0; s < used; ++s) {
+      const float* rec = rec0 + static_cast<size_t>(s) * (rank + 2);
+      if (rec[0] != -INFINITY) a = __fmaf_rn(rec[2 + d], expf(__fsub_rn(rec[0], m)), a);
+    }
+    out[static_cast<size_t>(r) * o_stride + h * rank + d] = bw::from_f<act_t>(__fmul_rn(a, inv));
+  }
+}
+
+size_t attention_smem(int rank, int rot_dim, int queries) {
+  const int dk = rank + rot_dim;
+  return (static_cast<size_t>(kKeys) * (dk + 1) + static_cast<size_t>(queries) * dk) * sizeof(float);
+}
+
+template <typename K>
+int raise_smem(K kernel, size_t smem) {
+  if (smem <= 48 * 1024) return 0;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  if (e != cudaSuccess) {
+    bw::set_error("latent attention: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
+    return static_cast<int>(e);
+  }
+  return 0;
+}
+
+constexpr int kQueriesPerWarp = 4;
+
+}  // namespace
+
+BW_API int BW_FN(latent_store)(const float* d, int d_stride, const float* w, float eps, const int* pos,
+                               const int* row_seq, const float* cos_t, const float* sin_t, int pairs,
+                               const int* block_table, int max_blocks, act_t* cache, int n, int rank, int rot_dim,
+                               int page, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (rank <= 0 || rot_dim < 0 || 2 * pairs > rot_dim || (pairs > 0 && !cos_t)) {
+    bw::set_error("latent_store: rank %d, rotated part %d, %d pairs", rank, rot_dim, pairs);
+    return -1;
+  }
+  bw::launch_pdl(latent_store_kernel, dim3(n), dim3(128), 0, stream, d, d_stride, w, eps, pos, row_seq, cos_t, sin_t,
+                 pairs, block_table, max_blocks, cache, rank, rot_dim, page);
+  return bw::launch_status();
+}
+
+BW_API int BW_FN(rotate_heads)(const act_t* q, int q_stride, int head_stride, int offset, act_t* out, int o_stride,
+                               int out_head_stride, int out_offset, int n, int heads, int rot_dim, int pairs,
+                               const int* pos, const float* cos_t, const float* sin_t, cudaStream_t stream) {
+  if (n <= 0 || heads <= 0 || rot_dim <= 0) return 0;
+  if (2 * pairs > rot_dim || (pairs > 0 && !cos_t) || heads > 65535) {
+    bw::set_error("rotate_heads: %d heads, rotated part %d, %d pairs", heads, rot_dim, pairs);
+    return -1;
+  }
+  bw::launch_pdl(rotate_heads_kernel, dim3(n, heads), dim3(64), 0, stream, q, q_stride, head_stride, offset, out,
+                 o_stride, out_head_stride, out_offset, rot_dim, pairs, pos, cos_t, sin_t);
+  return bw::launch_status();
+}
+
+// Rows of one sequence that a query tile of this many heads holds (the tile height the caller
+// prepares), and the heads a block takes.
+BW_API int BW_FN(latent_attention_tile_rows)(int heads) {
+  const int q = kWarps * kQueriesPerWarp;
+  return heads >= q ? 1 : q / heads;
+}
+
+BW_API int BW_FN(latent_attention)(const act_t* q, int q_stride, const act_t* cache, const int* block_table,
+                                   int max_blocks, const int* tile_seq, const int* tile_row0, const int* tile_rows,
+                                   int tiles, const int* seq_pos0, const int* seq_row0, act_t* out, int o_stride,
+                                   int heads, int rank, int rot_dim, int page, int window, float scale,
+                                   cudaStream_t stream) {
+  if (tiles <= 0) return 0;
+  const int q_max = kWarps * kQueriesPerWarp;
+  const int hb = heads < q_max ? heads : q_max;
+  const size_t smem = attention_smem(rank, rot_dim, q_max);
+  if (rank > 512 || smem > 200 * 1024) {
+    bw::set_error("latent attention: latent size %d with rotated part %d is beyond the kernel (512, %zu bytes)", rank,
+                  rot_dim, smem);
+    return -1;
+  }
+  dim3 grid(tiles, (heads + hb - 1) / hb);
+#define BW_LAUNCH(ACC)                                                                                              \
+  {                                                                                                                 \
+    auto kernel = latent_attention_kernel<ACC, kQueriesPerWarp>;                                                    \
+    if (int rc = raise_smem(kernel, smem)) return rc;                                                               \
+    bw::launch_pdl(kernel, grid, dim3(kThreads), smem, stream, q, q_stride, cache, block_table, max_blocks, tile_seq, \
+                   tile_row0, tile_rows, seq_pos0, seq_row0, out, o_stride, heads, hb, rank, rot_dim, page, window, \
+                   scale);                                                                                          \
+  }
+  if (rank <= 128) BW_LAUNCH(4) else if (rank <= 256) BW_LAUNCH(8) else BW_LAUNCH(16)
+#undef BW_LAUNCH
+  return bw::launch_status();
+}
+
+// The split over keys for steps of single rows. `max_keys` bounds pos + 1 over the step; the
+// span is chosen from it and from the number of rows so that the step fills the machine, and is
+// a multiple of 32. Scratch: n * heads * spans * (rank + 2) floats.
+BW_API int BW_FN(latent_attention_spans)(int n, int heads, int max_keys, int* span_out) {
+  const int head_blocks = (heads + kWarps - 1) / kWarps;
+  int want = (2 * 148 + n * head_blocks - 1) / (n * head_blocks);  // spans per row for two blocks per SM
+  if (want < 1) want = 1;
+  int span = (max_keys + want - 1) / want;
+  span = (span + 127) / 128 * 128;  // at least four tiles per block
+  *span_out = span;
+  return (max_keys + span - 1) / span;
+}
+
+BW_API int BW_FN(latent_attention_split)(const act_t* q, int q_stride, const act_t* cache, const int* block_table,
+                                         int max_blocks, const int* row_seq, const int* pos, act_t* out, int o_stride,
+                                         int n, int heads, int rank, int rot_dim, int page, int window, float scale,
+                                         int max_keys, float* scratch, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  int span = 0;
+  const int spans = BW_FN(latent_attention_spans)(n, heads, max_keys, &span);
+  const size_t smem = attention_smem(rank, rot_dim, kWarps);
+  if (rank > 512 || smem > 200 * 1024 || spans > 65535) {
+    bw::set_error("latent attention: latent size %d with rotated part %d is beyond the kernel", rank, rot_dim);
+    return -1;
+  }
+  dim3 grid(n, spans, (heads + kWarps - 1) / kWarps);
+#define BW_LAUNCH(ACC)                                                                                               \
+  {                                                                                                                  \
+    auto kernel = latent_attention_split_kernel<ACC>;                                                                \
+    if (int rc = raise_smem(kernel, smem)) return rc;                                                                \
+    bw::launch_pdl(kernel, grid, dim3(kThreads), smem, stream, q, q_stride, cache, block_table, max_blocks, row_seq,  \
+                   pos, scratch, spans, span, heads, rank, rot_dim, page, window, scale);                            \
+  }
+  if (rank <= 128) BW_LAUNCH(4) else if (rank <= 256) BW_LAUNCH(8) else BW_LAUNCH(16)
+#undef BW_LAUNCH
+  if (int rc = bw::launch_status()) return rc;
+  bw::launch_pdl(latent_attention_merge_kernel, dim3(n, heads), dim3(128), 0, stream, scratch, pos, spans, span, heads,
+                 rank, out, o_stride);
+  return bw::launch_status();
+}

@@ -1,0 +1,342 @@
+// A feed-forward of many small experts of which a row uses a few, and products per group.
+//
+//  * route: from a row's router logits (float32) to its experts and their weights. Scores are
+//    sigmoid(z); a correction per expert is added for the choice only; the experts form equal
+//    groups of neighbours, a group counts as the sum of its two largest choice scores, and only
+//    the experts of the best groups can be chosen; the weights are the chosen experts' scores
+//    times a constant.
+//  * group_rows: (row, choice) pairs listed expert by expert, with the tiles of the grouped
+//    product that follows.
+//  * grouped_linear: out[i] = x[source(i)] W_g^T for the list entries i of every group g, W
+//    stored [groups, n, k]. With a list the groups are the experts (rows of unequal number);
+//    without, every group takes every row and reads and writes its own columns (one product per
+//    head). An output is one chain of fused multiply-adds over k in ascending order, whatever
+//    tile it sits in.
+//  * glu_clamped: y = g' sigmoid(alpha g') (u' + 1), g' = min(g, limit), u' = clamp(u, +-limit).
+//  * combine: x += d + sum_j weight_j * y[place of (row, j)], the sum in the order of choice.
+#include "bw_act.cuh"
+
+#include <math.h>
+
+namespace {
+
+// ---------------------------------------------------------------------------------------
+// One warp per row. Shared memory per warp: scores s[E], choice scores c[E] (taken experts are
+// set to -inf as the choice goes on), group scores [groups].
+__global__ void __launch_bounds__(128)
+route_kernel(const float* __restrict__ z, const float* __restrict__ correction, int n, int experts, int groups,
+             int keep, int top, float weight_scale, int* __restrict__ chosen, float* __restrict__ weights) {
+  bw::pdl_enter();
+  extern __shared__ float sm[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int r = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (r >= n) return;
+  float* s = sm + static_cast<size_t>(warp) * (2 * experts + groups);
+  float* c = s + experts;
+  float* gs = c + experts;
+  const float* zr = z + static_cast<size_t>(r) * experts;
+  for (int e = lane; e < experts; e += 32) {
+    const float v = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-zr[e])));
+    s[e] = v;
+    c[e] = __fadd_rn(v, correction ? correction[e] : 0.0f);
+  }
+  __syncwarp();
+  const int per = experts / groups;
+  if (keep < groups) {
+    for (int g = lane; g < groups; g += 32) {
+      float a = -INFINITY, b = -INFINITY;  // the two largest of the group
+      for (int e = g * per; e < (g + 1) * per; ++e) {
+        const float v = c[e];
+        if (v > a) b = a, a = v;
+        else if (v > b) b = v;
+      }
+      gs[g] = per > 1 ? __fadd_rn(a, b) : a;
+    }
+    __syncwarp();
+    // the groups that stay are taken out of gs one by one (marked +inf); the rest lose their experts
+    for (int k = 0; k < keep; ++k) {
+      float best = -INFINITY;
+      int at = 0x7fffffff;
+      for (int g = lane; g < groups; g += 32) {
+        const float v = gs[g];
+        if (v != INFINITY && (v > best || at == 0x7fffffff)) best = v, at = g;
+      }
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+        if (oa != 0x7fffffff && (at == 0x7fffffff || ob > best || (ob == best && oa < at))) best = ob, at = oa;
+      }
+      if (lane == 0 && at != 0x7fffffff) gs[at] = INFINITY;
+      __syncwarp();
+    }
+    for (int e = lane; e < experts; e += 32)
+      if (gs[e / per] != INFINITY) c[e] = -INFINITY;
+    __syncwarp();
+  }
+  // a taken expert is marked by a negative score (scores lie in (0, 1)) once its weight is read
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY;
+    int at = 0x7fffffff;
+    for (int e = lane; e < experts; e += 32) {
+      const float v = c[e];
+      if (s[e] >= 0.0f && (at == 0x7fffffff || v > best)) best = v, at = e;
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+      if (oa != 0x7fffffff && (at == 0x7fffffff || ob > best || (ob == best && oa < at))) best = ob, at = oa;
+    }
+    if (lane == 0) {
+      chosen[static_cast<size_t>(r) * top + k] = at;
+      weights[static_cast<size_t>(r) * top + k] = __fmul_rn(s[at], weight_scale);
+      s[at] = -1.0f;  // taken
+    }
+    __syncwarp();
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// One block. pairs = n * top entries of `chosen`. Outputs: group_off[E + 1] (where each
+// expert's list begins), tile_prefix[E + 1] (tiles of `tile_rows` list entries before each
+// expert), order[pairs] (the pairs expert by expert, ascending inside an expert) and
+// place[pairs] (where a pair stands in that order).
+__global__ void __launch_bounds__(1024)
+group_rows_kernel(const int* __restrict__ chosen, int pairs, int experts, int tile_rows, int* __restrict__ group_off,
+                  int* __restrict__ tile_prefix, int* __restrict__ order, int* __restrict__ place) {
+  bw::pdl_enter();
+  extern __shared__ int cnt[];  // [experts + 1]
+  for (int e = threadIdx.x; e <= experts; e += blockDim.x) cnt[e] = 0;
+  __syncthreads();
+  for (int p = threadIdx.x; p < pairs; p += blockDim.x) atomicAdd(&cnt[chosen[p]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int rows = 0, tiles = 0;
+    for (int e = 0; e < experts; ++e) {
+      const int c = cnt[e];
+      group_off[e] = rows, tile_prefix[e] = tiles, cnt[e] = rows;
+      rows += c, tiles += (c + tile_rows - 1) / tile_rows;
+    }
+    group_off[experts] = rows, tile_prefix[experts] = tiles;
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  for (int e = warp; e < experts; e += warps) {
+    int at = cnt[e];
+    for (int p0 = 0; p0 < pairs; p0 += 32) {
+      const int p = p0 + lane;
+      const bool mine = p < pairs && chosen[p] == e;
+      const unsigned mask = __ballot_sync(0xffffffffu, mine);
+      if (mine) {
+        const int i = at + __popc(mask & ((1u << lane) - 1u));
+        order[i] = p, place[p] = i;
+      }
+      at += __popc(mask);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// The grouped product: tiles of 64 list entries x 64 outputs, k in steps of 16, 256 threads with
+// 4 x 4 outputs each.
+constexpr int kTile = 64, kStep = 16;
+
+template <typename OutT>
+__global__ void __launch_bounds__(256)
+grouped_linear_kernel(const act_t* __restrict__ x, int x_stride, int x_group_cols, const int* __restrict__ order,
+                      int order_div, const act_t* __restrict__ w, OutT* out, int o_stride, int o_group_cols,
+                      const int* __restrict__ group_off, const int* __restrict__ tile_prefix, int uniform_rows,
+                      int groups, int n, int k) {
+  bw::pdl_enter();
+  __shared__ float xs[kStep][kTile + 1];
+  __shared__ float ws[kStep][kTile + 1];
+  __shared__ int s_group;
+  int g, i0, i_end;
+  if (group_off) {
+    if (threadIdx.x == 0) {
+      int found = -1;
+      const int t = blockIdx.x;
+      if (t < tile_prefix[groups]) {
+        int lo = 0, hi = groups - 1;  // the last group whose first tile is at or before t and that has tiles
+        while (lo < hi) {
+          const int mid = (lo + hi + 1) >> 1;
+          if (tile_prefix[mid] <= t) lo = mid; else hi = mid - 1;
+        }
+        found = lo;
+      }
+      s_group = found;
+    }
+    __syncthreads();
+    g = s_group;
+    if (g < 0) return;
+    i0 = group_off[g] + (blockIdx.x - tile_prefix[g]) * kTile;
+    i_end = group_off[g + 1];
+  } else {
+    const int tiles = (uniform_rows + kTile - 1) / kTile;
+    g = blockIdx.x / tiles;
+    i0 = (blockIdx.x - g * tiles) * kTile;
+    i_end = uniform_rows;
+  }
+  const int j0 = blockIdx.y * kTile;
+  const act_t* wg = w + static_cast<size_t>(g) * n * k;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;  // outputs (ty * 4 + a, tx * 4 + b)
+  // what this thread loads each step: entry (threadIdx.x / 16) + 16 q of the tile, k index threadIdx.x % 16
+  const int lk = threadIdx.x & 15, lr = threadIdx.x >> 4;
+  const act_t* xrow[4];
+  const act_t* wrow[4];
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const int i = i0 + lr + 16 * q;
+    xrow[q] = nullptr;
+    if (i < i_end) {
+      const int src = order ? order[i] / order_div : i;
+      xrow[q] = x + static_cast<size_t>(src) * x_stride + (group_off ? 0 : g * x_group_cols);
+    }
+    const int j = j0 + lr + 16 * q;
+    wrow[q] = j < n ? wg + static_cast<size_t>(j) * k : nullptr;
+  }
+  float acc[4][4];
+#pragma unroll
+  for (int a = 0; a < 4; ++a)
+#pragma unroll
+    for (int b = 0; b < 4; ++b) acc[a][b] = 0.0f;
+  for (int k0 = 0; k0 < k; k0 += kStep) {
+    const int kk = k0 + lk;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      xs[lk][lr + 16 * q] = (xrow[q] && kk < k) ? bw::to_f(xrow[q][kk]) : 0.0f;
+      ws[lk][lr + 16 * q] = (wrow[q] && kk < k) ? bw::to_f(wrow[q][kk]) : 0.0f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int s = 0; s < kStep; ++s) {
+      float xv[4], wv[4];
+#pragma unroll
+      for (int a = 0; a < 4; ++a) xv[a] = xs[s][ty * 4 + a], wv[a] = ws[s][tx * 4 + a];
+#pragma unroll
+      for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) acc[a][b] = __fmaf_rn(xv[a], wv[b], acc[a][b]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int a = 0; a < 4; ++a) {
+    const int i = i0 + ty * 4 + a;
+    if (i >= i_end) continue;
+    OutT* orow = out + static_cast<size_t>(i) * o_stride + (group_off ? 0 : g * o_group_cols);
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+      const int j = j0 + tx * 4 + b;
+      if (j < n) orow[j] = bw::from_f<OutT>(acc[a][b]);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+__global__ void glu_clamped_kernel(const act_t* __restrict__ gate_up, act_t* __restrict__ out, int inter, float limit,
+                                   float alpha) {
+  bw::pdl_enter();
+  const int r = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= inter) return;
+  const act_t* row = gate_up + static_cast<size_t>(r) * 2 * inter;
+  const float g = fminf(bw::to_f(row[c]), limit);
+  const float u = fminf(fmaxf(bw::to_f(row[inter + c]), -limit), limit);
+  const float sig = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-__fmul_rn(alpha, g))));
+  out[static_cast<size_t>(r) * inter + c] = bw::from_f<act_t>(__fmul_rn(__fmul_rn(g, sig), __fadd_rn(u, 1.0f)));
+}
+
+// x[r] += d[r] + sum_j weights[r][j] * y[place[r * top + j]]; d may be null.
+__global__ void combine_kernel(float* x, const float* __restrict__ d, const float* __restrict__ y,
+                               const int* __restrict__ place, const float* __restrict__ weights, int top, int width) {
+  bw::pdl_enter();
+  const int r = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= width) return;
+  float s = 0.0f;
+  for (int j = 0; j < top; ++j) {
+    const size_t p = static_cast<size_t>(r) * top + j;
+    s = __fmaf_rn(weights[p], y[static_cast<size_t>(place[p]) * width + c], s);
+  }
+  const size_t o = static_cast<size_t>(r) * width + c;
+  if (d) s = __fadd_rn(d[o], s);
+  x[o] = __fadd_rn(x[o], s);
+}
+
+}  // namespace
+
+BW_API int BW_FN(route)(const float* z, const float* correction, int n, int experts, int groups, int keep, int top,
+                        float weight_scale, int* chosen, float* weights, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (experts <= 0 || groups <= 0 || experts % groups || keep <= 0 || keep > groups || top <= 0 ||
+      top > keep * (experts / groups)) {
+    bw::set_error("route: %d experts in %d groups of which %d stay cannot give %d choices", experts, groups, keep, top);
+    return -1;
+  }
+  const int warps = 4;
+  const size_t smem = static_cast<size_t>(warps) * (2 * experts + groups) * sizeof(float);
+  if (smem > 48 * 1024) {
+    bw::set_error("route: %d experts are beyond the kernel", experts);
+    return -1;
+  }
+  bw::launch_pdl(route_kernel, dim3((n + warps - 1) / warps), dim3(warps * 32), smem, stream, z, correction, n, experts,
+                 groups, keep, top, weight_scale, chosen, weights);
+  return bw::launch_status();
+}
+
+BW_API int BW_FN(grouped_tile_rows)() { return kTile; }
+
+BW_API int BW_FN(group_rows)(const int* chosen, int pairs, int experts, int* group_off, int* tile_prefix, int* order,
+                             int* place, cudaStream_t stream) {
+  if (pairs <= 0) return 0;
+  if (experts <= 0 || experts > 8192) {
+    bw::set_error("group_rows: %d experts", experts);
+    return -1;
+  }
+  bw::launch_pdl(group_rows_kernel, dim3(1), dim3(1024), static_cast<size_t>(experts + 1) * sizeof(int), stream, chosen,
+                 pairs, experts, kTile, group_off, tile_prefix, order, place);
+  return bw::launch_status();
+}
+
+// With a list (group_off, tile_prefix, order from group_rows; `rows` = its length): entry i of
+// group g reads x[order[i] / order_div] (order null: x[i]) and writes out[i]. Without (group_off
+// null): every group takes rows 0 .. rows-1, reads columns g * x_group_cols .. and writes columns
+// g * o_group_cols ...
+BW_API int BW_FN(grouped_linear)(const act_t* x, int x_stride, int x_group_cols, const int* order, int order_div,
+                                 const act_t* w, void* out, int out_is_f32, int o_stride, int o_group_cols,
+                                 const int* group_off, const int* tile_prefix, int rows, int groups, int n, int k,
+                                 cudaStream_t stream) {
+  if (rows <= 0 || groups <= 0 || n <= 0) return 0;
+  if (k <= 0 || order_div <= 0) {
+    bw::set_error("grouped_linear: inner size %d", k);
+    return -1;
+  }
+  const long long tiles = group_off ? (rows + kTile - 1) / kTile + groups
+                                    : static_cast<long long>(groups) * ((rows + kTile - 1) / kTile);
+  dim3 grid(static_cast<unsigned>(tiles), (n + kTile - 1) / kTile);
+  if (tiles > 0x7fffffffLL || grid.y > 65535u) {
+    bw::set_error("grouped_linear: %lld tiles exceed the grid", tiles);
+    return -1;
+  }
+  if (out_is_f32)
+    bw::launch_pdl(grouped_linear_kernel<float>, grid, dim3(256), 0, stream, x, x_stride, x_group_cols, order, order_div,
+                   w, static_cast<float*>(out), o_stride, o_group_cols, group_off, tile_prefix, rows, groups, n, k);
+  else
+    bw::launch_pdl(grouped_linear_kernel<act_t>, grid, dim3(256), 0, stream, x, x_stride, x_group_cols, order, order_div,
+                   w, static_cast<act_t*>(out), o_stride, o_group_cols, group_off, tile_prefix, rows, groups, n, k);
+  return bw::launch_status();
+}
+
+BW_API int BW_FN(glu_clamped)(const act_t* gate_up, act_t* out, int n, int inter, float limit, float alpha,
+                              cudaStream_t stream) {
+  if (n <= 0 || inter <= 0) return 0;
+  bw::launch_pdl(glu_clamped_kernel, dim3(n, (inter + 255) / 256), dim3(256), 0, stream, gate_up, out, inter, limit, alpha);
+  return bw::launch_status();
+}
+
+BW_API int BW_FN(combine)(float* x, const float* d, const float* y, const int* place, const float* weights, int n,
+                          int top, int width, cudaStream_t stream) {
+  if (n <= 0 || width <= 0) return 0;
+  bw::launch_pdl(combine_kernel, dim3(n, (width + 255) / 256), dim3(256), 0, stream, x, d, y, place, weights, top, width);
+  return bw::launch_status();
+}

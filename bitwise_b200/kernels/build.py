@@ -32,6 +32,12 @@ KERNEL_SETS: Dict[str, List[tuple]] = {
              ("bf16_gemm_rows.cu", [])],
     # compiled once per head size, with -DBW_HEAD_DIM=<n>
     "bf16_attn": [("common.cu", []), ("bf16_attention.cu", []), ("bf16_attention_tc.cu", [])],
+    # parts that only some architectures have (layer norm, latent attention, routed feed-forward):
+    # one source per part, compiled for either precision; loaded when a model first asks
+    "f32_parts": [("common.cu", []), ("layer_norm.cu", ["-DBW_ACT_BF16=0"]), ("latent_attention.cu", ["-DBW_ACT_BF16=0"]),
+                  ("routed_ffn.cu", ["-DBW_ACT_BF16=0"])],
+    "bf16_parts": [("common.cu", []), ("layer_norm.cu", ["-DBW_ACT_BF16=1"]), ("latent_attention.cu", ["-DBW_ACT_BF16=1"]),
+                   ("routed_ffn.cu", ["-DBW_ACT_BF16=1"])],
 }
 
 # head sizes whose attention library a full build prepares (others are compiled when a model asks)
@@ -82,8 +88,9 @@ def _set_sources(kind: str, defines: Sequence[str]):
 def _digest(kind: str, defines: Sequence[str]) -> str:
     h = hashlib.sha256()
     h.update(" ".join(ARCH_FLAGS + BASE_FLAGS + list(defines)).encode())
-    for f in sorted(os.listdir(CSRC)):
-        if f.endswith((".cu", ".cuh", ".h")):
+    own = {f for f, _ in KERNEL_SETS[kind]}
+    for f in sorted(os.listdir(CSRC)):  # the set's own sources and every header
+        if f in own or f.endswith((".cuh", ".h")):
             h.update(f.encode())
             with open(os.path.join(CSRC, f), "rb") as fh:
                 h.update(fh.read())
@@ -208,6 +215,6 @@ def ensure_host_built(verbose: bool = True) -> str:
 def build_all(verbose: bool = True) -> List[str]:
     """Compile every kernel set (what a 'does it build' check wants)."""
     out = [ensure_host_built(verbose)]
-    out += [ensure_built(k, (), verbose) for k in ("f32", "bf16")]
+    out += [ensure_built(k, (), verbose) for k in ("f32", "bf16", "f32_parts", "bf16_parts")]
     out += [ensure_built("bf16_attn", (f"BW_HEAD_DIM={hd}",), verbose) for hd in DEFAULT_HEAD_DIMS]
     return out

@@ -308,7 +308,7 @@ class KernelOps:
             dev = torch.device("cuda", self._device_index())
             self._failure_word = torch.zeros(1, dtype=torch.int32, device=dev)
             self._failure_host = torch.zeros(1, dtype=torch.int32, pin_memory=True)
-            for lib in [self.lib] + list(self._attn_libs.values()):
+            for lib in [self.lib] + list(self._attn_libs.values()) + [l for l in [getattr(self, "_parts", None)] if l]:
                 lib.bw_set_failure_word(_p(self._failure_word))
         return self._failure_word, self._failure_host
 
@@ -573,6 +573,245 @@ class KernelOps:
         if gate_up.shape[1] != 2 * inter or gate_up.shape[0] != n:
             raise KernelError("swiglu: input is not [rows, 2 * intermediate]")
         self._call(f"bw_{self.kind}_swiglu", _p(gate_up), _p(out), _c_int(n), _c_int(inter), self._stream())
+
+    # -- parts that only some architectures have (their library is loaded at first use) ------
+    def _parts_lib(self):
+        lib = getattr(self, "_parts", None)
+        if lib is None:
+            path = build.ensure_built(f"{self.kind}_parts", (), self._verbose_build)
+            try:
+                lib = ctypes.CDLL(path)
+            except OSError as e:
+                raise KernelError(f"cannot load the kernel library {path}: {e}") from None
+            lib.bw_last_error.restype = ctypes.c_char_p
+            if self._failure_word is not None:
+                lib.bw_set_failure_word(_p(self._failure_word))
+            self._parts = lib
+            self._parts_fns = {}
+        return lib
+
+    def _pcall(self, name: str, *args, launches: int = 1) -> None:
+        lib = self._parts_lib()
+        fn = self._parts_fns.get(name)
+        if fn is None:
+            fn = getattr(lib, f"bw_{self.kind}_{name}")
+            fn.restype = _c_int
+            self._parts_fns[name] = fn
+        rc = fn(*args)
+        if rc != 0:
+            raise KernelError(f"{name} failed ({rc}): " + lib.bw_last_error().decode("utf-8", "replace"))
+        self.launches += launches
+
+    def layernorm(self, x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
+                  rows: Optional[torch.Tensor] = None, weight2: Optional[torch.Tensor] = None,
+                  out2: Optional[torch.Tensor] = None) -> None:
+        """out[r] = (x[s] - mean) / sqrt(var + eps) * weight with s = rows[r] or r; x float32, out
+        float32 (it may be x itself) or act_dtype.  With ``weight2`` and ``out2`` a second output
+        of the same row statistics."""
+        n, width = out.shape
+        _need(x, torch.float32, "layernorm x", 2)
+        _need(weight, torch.float32, "layernorm weight", 1)
+        if out.dtype not in (torch.float32, self.act_dtype):
+            raise KernelError(f"layernorm: out is {out.dtype}")
+        _need(out, out.dtype, "layernorm out", 2)
+        if x.shape[1] != width or weight.shape[0] != width:
+            raise KernelError("layernorm: widths differ")
+        if (weight2 is None) != (out2 is None):
+            raise KernelError("layernorm: a second weight needs a second output")
+        if out2 is not None:
+            _need(weight2, torch.float32, "layernorm weight2", 1)
+            _need(out2, out.dtype, "layernorm out2", 2)
+            if tuple(out2.shape) != (n, width) or weight2.shape[0] != width:
+                raise KernelError("layernorm: the second output's shape differs")
+        if rows is not None:
+            _need(rows, torch.int32, "layernorm rows")
+        self._pcall("layernorm", _p(x), _p(weight), _p(weight2), _p(out), _p(out2),
+                    _c_int(int(out.dtype == torch.float32)), _p(rows), _c_int(n), _c_int(width), _c_float(eps),
+                    self._stream())
+
+    def add_rows(self, x: torch.Tensor, d: torch.Tensor) -> None:
+        """x += d (float32, same shape)."""
+        _need(x, torch.float32, "add_rows x")
+        _need(d, torch.float32, "add_rows d")
+        if x.shape != d.shape:
+            raise KernelError("add_rows: shapes differ")
+        self._pcall("add_rows", _p(x), _p(d), ctypes.c_longlong(x.numel()), self._stream())
+
+    def latent_store(self, d: torch.Tensor, weight: torch.Tensor, eps: float, pos: torch.Tensor, row_seq: torch.Tensor,
+                     cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], block_table: torch.Tensor,
+                     cache: torch.Tensor, rank: int, rot_dim: int) -> None:
+        """For every row of ``d`` (float32 [n, rank + rot_dim]): the first ``rank`` entries divided by
+        their root mean square (eps inside the root) times ``weight``, the last ``rot_dim`` turned pair
+        by pair (2i with 2i+1) by row ``pos`` of the tables, both stored at the row's place in ``cache``
+        [pages, page, rank + rot_dim]."""
+        n = d.shape[0]
+        _need(d, torch.float32, "latent_store d", 2)
+        _need(weight, torch.float32, "latent_store weight", 1)
+        _need(pos, torch.int32, "latent_store pos")
+        _need(row_seq, torch.int32, "latent_store row_seq")
+        _need(block_table, torch.int32, "latent_store block_table", 2)
+        _need(cache, self.act_dtype, "latent_store cache", 3)
+        if d.shape[1] != rank + rot_dim or cache.shape[2] != rank + rot_dim or weight.shape[0] != rank:
+            raise KernelError("latent_store: widths do not fit rank + rot_dim")
+        pairs = self._check_tables(cos, sin, rot_dim, "latent_store")
+        self._pcall("latent_store", _p(d), _c_int(d.shape[1]), _p(weight), _c_float(eps), _p(pos), _p(row_seq), _p(cos),
+                    _p(sin), _c_int(pairs), _p(block_table), _c_int(block_table.shape[1]), _p(cache), _c_int(n),
+                    _c_int(rank), _c_int(rot_dim), _c_int(cache.shape[1]), self._stream())
+
+    @staticmethod
+    def _check_tables(cos, sin, rot_dim: int, what: str) -> int:
+        if cos is None:
+            return 0
+        _need(cos, torch.float32, what + " cos", 2)
+        _need(sin, torch.float32, what + " sin", 2)
+        if cos.shape != sin.shape or 2 * cos.shape[1] > rot_dim:
+            raise KernelError(f"{what}: the tables turn {2 * cos.shape[1]} entries of {rot_dim}")
+        return int(cos.shape[1])
+
+    def rotate_heads(self, q: torch.Tensor, heads: int, head_stride: int, offset: int, rot_dim: int, out: torch.Tensor,
+                     out_head_stride: int, out_offset: int, pos: torch.Tensor, cos: Optional[torch.Tensor],
+                     sin: Optional[torch.Tensor]) -> None:
+        """out[r, h * out_head_stride + out_offset + i] = the entries q[r, h * head_stride + offset + i],
+        i < rot_dim, turned pair by pair (2i with 2i+1) by row pos[r] of the tables."""
+        n = q.shape[0]
+        _need(q, self.act_dtype, "rotate_heads q", 2)
+        _need(out, self.act_dtype, "rotate_heads out", 2)
+        _need(pos, torch.int32, "rotate_heads pos")
+        if (heads - 1) * head_stride + offset + rot_dim > q.shape[1] or \
+                (heads - 1) * out_head_stride + out_offset + rot_dim > out.shape[1] or out.shape[0] != n:
+            raise KernelError("rotate_heads: the heads do not fit the rows")
+        pairs = self._check_tables(cos, sin, rot_dim, "rotate_heads")
+        self._pcall("rotate_heads", _p(q), _c_int(q.shape[1]), _c_int(head_stride), _c_int(offset), _p(out),
+                    _c_int(out.shape[1]), _c_int(out_head_stride), _c_int(out_offset), _c_int(n), _c_int(heads),
+                    _c_int(rot_dim), _c_int(pairs), _p(pos), _p(cos), _p(sin), self._stream())
+
+    def latent_attention_tile_rows(self, heads: int) -> int:
+        """Rows of one sequence per query tile that ``latent_attention`` wants prepared."""
+        fn = getattr(self._parts_lib(), f"bw_{self.kind}_latent_attention_tile_rows")
+        return int(fn(_c_int(heads)))
+
+    def latent_attention(self, q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, out: torch.Tensor,
+                         heads: int, rank: int, rot_dim: int, scale: float, batch, window: int = 0) -> None:
+        """out[r, h] = sum_j softmax_j(q[r, h] . cache[j] * scale) cache[j][:rank] over the cached
+        positions j <= pos[r] of row r's sequence (from pos - window + 1 on when window > 0).
+        q: [n, heads * (rank + rot_dim)] (the heads' key maps folded in, the rotated part turned),
+        cache: [pages, page, rank + rot_dim], out: [n, heads * rank]."""
+        n = q.shape[0]
+        dk = rank + rot_dim
+        _need(q, self.act_dtype, "latent_attention q", 2)
+        _need(cache, self.act_dtype, "latent_attention cache", 3)
+        _need(out, self.act_dtype, "latent_attention out", 2)
+        _need(block_table, torch.int32, "latent_attention block_table", 2)
+        if q.shape[1] != heads * dk or cache.shape[2] != dk or tuple(out.shape) != (n, heads * rank):
+            raise KernelError("latent_attention: shapes do not fit heads * (rank + rot_dim)")
+        page = cache.shape[1]
+        t_seq, t_row0, t_rows, t_count = batch.query_tiles(self.latent_attention_tile_rows(heads))
+        if t_count == n and batch.max_keys > 256:
+            # single rows with long contexts: spread every row's keys over many blocks
+            lib = self._parts_lib()
+            span = _c_int(0)
+            spans = int(getattr(lib, f"bw_{self.kind}_latent_attention_spans")(_c_int(n), _c_int(heads),
+                                                                               _c_int(batch.max_keys), ctypes.byref(span)))
+            keys = (batch.max_keys + 2047) // 2048 * 2048  # sized so that it seldom grows
+            floats = n * heads * max(spans, (keys + span.value - 1) // span.value) * (rank + 2)
+            if self._attn_scratch is None or self._attn_scratch.numel() < floats:
+                self._retired.append(self._attn_scratch)  # a captured graph may still point at the old one
+                self._attn_scratch = torch.empty(floats, dtype=torch.float32, device=q.device)
+            self._pcall("latent_attention_split", _p(q), _c_int(q.shape[1]), _p(cache), _p(block_table),
+                        _c_int(block_table.shape[1]), _p(batch.row_seq), _p(batch.pos), _p(out), _c_int(out.shape[1]),
+                        _c_int(n), _c_int(heads), _c_int(rank), _c_int(rot_dim), _c_int(page), _c_int(window),
+                        _c_float(scale), _c_int(batch.max_keys), _p(self._attn_scratch), self._stream(), launches=2)
+            return
+        self._pcall("latent_attention", _p(q), _c_int(q.shape[1]), _p(cache), _p(block_table),
+                    _c_int(block_table.shape[1]), _p(t_seq), _p(t_row0), _p(t_rows), _c_int(t_count), _p(batch.seq_pos0),
+                    _p(batch.seq_row0), _p(out), _c_int(out.shape[1]), _c_int(heads), _c_int(rank), _c_int(rot_dim),
+                    _c_int(page), _c_int(window), _c_float(scale), self._stream())
+
+    def route(self, logits: torch.Tensor, correction: Optional[torch.Tensor], groups: int, keep: int, top: int,
+              weight_scale: float, chosen: torch.Tensor, weights: torch.Tensor) -> None:
+        """Per row of ``logits`` (float32 [n, experts]): scores sigmoid(z); the ``top`` experts with
+        the largest score + correction among the experts of the ``keep`` best of ``groups`` equal
+        groups of neighbours (a group counts as the sum of its two largest corrected scores);
+        chosen int32 [n, top], weights float32 [n, top] = score * weight_scale."""
+        n, experts = logits.shape
+        _need(logits, torch.float32, "route logits", 2)
+        _need(chosen, torch.int32, "route chosen", 2)
+        _need(weights, torch.float32, "route weights", 2)
+        if correction is not None:
+            _need(correction, torch.float32, "route correction", 1)
+        if tuple(chosen.shape) != (n, top) or tuple(weights.shape) != (n, top):
+            raise KernelError("route: outputs are not [rows, top]")
+        self._pcall("route", _p(logits), _p(correction), _c_int(n), _c_int(experts), _c_int(groups), _c_int(keep),
+                    _c_int(top), _c_float(weight_scale), _p(chosen), _p(weights), self._stream())
+
+    def group_rows(self, chosen: torch.Tensor, experts: int, group_off: torch.Tensor, tile_prefix: torch.Tensor,
+                   order: torch.Tensor, place: torch.Tensor) -> None:
+        """The (row, choice) pairs of ``chosen`` listed expert by expert: group_off [experts + 1],
+        tile_prefix [experts + 1] (tiles of the grouped product before each expert), order [pairs]
+        (pair index = row * top + choice), place [pairs] (where a pair stands in ``order``)."""
+        pairs = chosen.numel()
+        for t_, what in ((chosen, "chosen"), (group_off, "group_off"), (tile_prefix, "tile_prefix"), (order, "order"),
+                         (place, "place")):
+            _need(t_, torch.int32, "group_rows " + what)
+        if group_off.numel() < experts + 1 or tile_prefix.numel() < experts + 1 or order.numel() < pairs or \
+                place.numel() < pairs:
+            raise KernelError("group_rows: an output is too small")
+        self._pcall("group_rows", _p(chosen), _c_int(pairs), _c_int(experts), _p(group_off), _p(tile_prefix), _p(order),
+                    _p(place), self._stream())
+
+    def grouped_linear(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, rows: int, x_group_cols: int = 0,
+                       o_group_cols: int = 0, lists=None, order_div: int = 1, gather: bool = True) -> None:
+        """One product per group with w [groups, n, k].  Without ``lists`` every group g takes rows
+        0 .. rows-1: out[r, g * o_group_cols + j] = sum_i x[r, g * x_group_cols + i] w[g, j, i].  With
+        ``lists`` = (group_off, tile_prefix, order) from ``group_rows`` entry i of group g reads row
+        order[i] // order_div of x (row i when ``gather`` is False) and writes row i of out; ``rows``
+        is then the length of the list."""
+        groups, n, k = w.shape
+        _need(x, self.act_dtype, "grouped_linear x", 2)
+        _need(w, self.act_dtype, "grouped_linear w", 3)
+        if out.dtype not in (torch.float32, self.act_dtype):
+            raise KernelError(f"grouped_linear: out is {out.dtype}")
+        _need(out, out.dtype, "grouped_linear out", 2)
+        if lists is None:
+            if (groups - 1) * x_group_cols + k > x.shape[1] or (groups - 1) * o_group_cols + n > out.shape[1] or \
+                    rows > x.shape[0] or rows > out.shape[0]:
+                raise KernelError("grouped_linear: the groups' columns do not fit the rows")
+            group_off = tile_prefix = order = None
+        else:
+            group_off, tile_prefix, order = lists
+            if x.shape[1] != k or out.shape[1] != n or rows > out.shape[0]:
+                raise KernelError("grouped_linear: widths differ from the weights'")
+            if not gather:
+                order = None
+        self._pcall("grouped_linear", _p(x), _c_int(x.shape[1]), _c_int(x_group_cols), _p(order), _c_int(order_div),
+                    _p(w), _p(out), _c_int(int(out.dtype == torch.float32)), _c_int(out.shape[1]), _c_int(o_group_cols),
+                    _p(group_off), _p(tile_prefix), _c_int(rows), _c_int(groups), _c_int(n), _c_int(k), self._stream())
+
+    def glu_clamped(self, gate_up: torch.Tensor, out: torch.Tensor, limit: float, alpha: float) -> None:
+        """out = g' * sigmoid(alpha * g') * (u' + 1) for rows laid out [gate | up], with
+        g' = min(g, limit) and u' = clamp(u, -limit, limit)."""
+        n, inter = out.shape
+        _need(gate_up, self.act_dtype, "glu_clamped gate_up", 2)
+        _need(out, self.act_dtype, "glu_clamped out", 2)
+        if gate_up.shape[1] != 2 * inter or gate_up.shape[0] != n:
+            raise KernelError("glu_clamped: input is not [rows, 2 * inner]")
+        self._pcall("glu_clamped", _p(gate_up), _p(out), _c_int(n), _c_int(inter), _c_float(limit), _c_float(alpha),
+                    self._stream())
+
+    def combine(self, x: torch.Tensor, d: Optional[torch.Tensor], y: torch.Tensor, place: torch.Tensor,
+                weights: torch.Tensor, top: int) -> None:
+        """x[r] += d[r] + sum_j weights[r, j] * y[place[r * top + j]] (float32; d may be None)."""
+        n, width = x.shape
+        _need(x, torch.float32, "combine x", 2)
+        _need(y, torch.float32, "combine y", 2)
+        _need(place, torch.int32, "combine place")
+        _need(weights, torch.float32, "combine weights", 2)
+        if d is not None:
+            _need(d, torch.float32, "combine d", 2)
+        if y.shape[1] != width or tuple(weights.shape) != (n, top) or (d is not None and d.shape != x.shape):
+            raise KernelError("combine: shapes differ")
+        self._pcall("combine", _p(x), _p(d), _p(y), _p(place), _p(weights), _c_int(n), _c_int(top), _c_int(width),
+                    self._stream())
 
 
 _OPS = {}

@@ -1,4 +1,5 @@
 from .decoder import DecoderModel, LayerRun, sequential_schedule
 from . import llama  # noqa: F401  (registers LlamaForCausalLM)
+from . import nuderax  # noqa: F401  (registers Nuderax)
 
 __all__ = ["DecoderModel", "LayerRun", "sequential_schedule"]

@@ -103,7 +103,7 @@ class DecoderModel:
     def tensor_aliases(self) -> Dict[str, str]:
         """Stored name -> declared tensor it must repeat: a tied head stored a second time."""
         if self.head.tied_to is not None:
-            return {f"{self.head.head_name}.weight": f"{self.embed_prefix}.{self.head.tied_to.name}.weight"}
+            return {f"{self.head.head_name}.weight": self.head.tied_to.tensor_name(self.embed_prefix)}
         return {}
 
     def prepare(self, ops) -> None:
@@ -122,7 +122,7 @@ class DecoderModel:
         parts = [self.embedding, self.head, self.head.norm] + list(self.position_encodings)
         for b in self.blocks:
             parts += [b, b.mixer, b.feed_forward, b.mixer_norm, b.ffn_norm]
-        return all(getattr(p, "graph_safe", False) for p in parts)
+        return all(getattr(p, "graph_safe", False) for p in parts if p is not None)
 
     def reserve_positions(self, positions: int) -> None:
         for pe in self.position_encodings:

@@ -1,9 +1,11 @@
 from .attention import GQAAttention
 from .base import (FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, FeedForward, Mixer, Norm, PagedKVNeed,
-                   PagedKVView, Part, PositionEncoding, SlotStateNeed, SlotStateView, StepContext, Workspace,
+                   PagedKVView, PagedLatentNeed, PagedLatentView, Part, PositionEncoding, SlotStateNeed, SlotStateView, StepContext, Workspace,
                    register_feed_forward, register_mixer, register_norm, register_position_encoding)
-from .block import PreNormBlock
+from .block import ParallelBlock, PreNormBlock
 from .embedding import OutputHead, TokenEmbedding
 from .mlp import SwiGLU
-from .norm import RMSNorm
+from .latent_attention import LatentAttention
+from .norm import LayerNorm, RMSNorm
 from .rope import RotaryEncoding, inverse_frequencies
+from .routed_ffn import ClampedGLU, RoutedFFN

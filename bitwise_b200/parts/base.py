@@ -33,6 +33,16 @@ class PagedKVNeed:
 
 
 @dataclass(frozen=True)
+class PagedLatentNeed:
+    """One vector per position for all heads, kept in pages: a latent of ``rank`` numbers from
+    which a mixer makes every head's keys and values, followed by ``rot_dim`` numbers of a
+    rotated key part that the heads share.  ``window`` as for :class:`PagedKVNeed`."""
+    rank: int
+    rot_dim: int
+    window: Optional[int] = None
+
+
+@dataclass(frozen=True)
 class SlotStateNeed:
     """State of fixed size per request, one slot each: ``shape`` elements of ``dtype``.
     A slot is handed out as the request that held it before left it: the mixer starts its state
@@ -49,6 +59,15 @@ class PagedKVView:
     """The cache of one layer run, as a mixer sees it during a step."""
     k: torch.Tensor            # [pages, kv_heads, page, head_dim]
     v: torch.Tensor
+    block_table: torch.Tensor  # int32 [step sequences, max blocks] of the layer's group
+    page_size: int
+    writable: bool = True      # False: the run reads another run's cache and stores nothing
+
+
+@dataclass
+class PagedLatentView:
+    """The latent cache of one layer run during a step."""
+    latent: torch.Tensor       # [pages, page, rank + rot_dim]
     block_table: torch.Tensor  # int32 [step sequences, max blocks] of the layer's group
     page_size: int
     writable: bool = True      # False: the run reads another run's cache and stores nothing

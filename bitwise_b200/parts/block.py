@@ -1,4 +1,5 @@
-"""The arrangement of a layer: pre-norm residual block.
+"""The arrangements of a layer: the pre-norm residual block, and the parallel block whose mixer
+and feed-forward read the same input.
 
 ``x += mixer(norm1(x)); x += feed_forward(norm2(x))`` (src/model.cpp:281-305).  The
 block owns nothing but its four parts and the sub-names under which their tensors are
@@ -55,3 +56,37 @@ class PreNormBlock(Part):
         self.mixer.forward(ctx, xn, x, cache)
         self.ffn_norm.forward(ctx, x, xn)
         self.feed_forward.forward(ctx, xn, x)
+
+
+class ParallelBlock(PreNormBlock):
+    """``x += mixer(norm1(x)) + feed_forward(norm2(x))``: both parts see the same x, their
+    outputs are added to each other first and to the stream last.  The mixer writes into a
+    float32 buffer, the feed-forward adds to it, and the sum goes into the stream; a feed-forward
+    that has ``forward_sum`` does the last two in its own last kernel.  ``feed_forward`` None: the
+    layer is its mixer alone."""
+
+    def _children(self, prefix: str):
+        kids = super()._children(prefix)
+        return [(p, n) for p, n in kids if p is not None]
+
+    def forward(self, ctx: StepContext, x: torch.Tensor, cache) -> None:
+        xn = ctx.workspace.rows("normed", ctx.n, self.width, ctx.act_dtype)
+        if self.feed_forward is None:
+            self.mixer_norm.forward(ctx, x, xn)
+            self.mixer.forward(ctx, xn, x, cache)
+            return
+        xn2 = ctx.workspace.rows("normed_b", ctx.n, self.width, ctx.act_dtype)
+        pair = getattr(self.mixer_norm, "forward_pair", None)
+        if pair is not None and type(self.ffn_norm) is type(self.mixer_norm):
+            pair(ctx, x, xn, self.ffn_norm, xn2)
+        else:
+            self.mixer_norm.forward(ctx, x, xn)
+            self.ffn_norm.forward(ctx, x, xn2)
+        delta = ctx.workspace.rows("block_sum", ctx.n, self.width, torch.float32)
+        self.mixer.forward(ctx, xn, delta, cache, accumulate=False)
+        fused = getattr(self.feed_forward, "forward_sum", None)
+        if fused is not None:
+            fused(ctx, xn2, delta, x)
+        else:
+            self.feed_forward.forward(ctx, xn2, delta)
+            ctx.ops.add_rows(x, delta)

@@ -18,21 +18,35 @@ from .base import Norm, Part, StepContext
 class TokenEmbedding(Part):
     graph_safe = True  # kernels only: a step through this part can be captured
 
-    def __init__(self, vocab: int, width: int, name: str = "embed_tokens"):
+    def __init__(self, vocab: int, width: int, name: str = "embed_tokens", tensor: Optional[str] = None,
+                 norm: Optional[Norm] = None, norm_tensor: Optional[str] = None):
+        """``tensor``: the table's full name where it is not ``<prefix>.<name>.weight``.  ``norm``:
+        a norm applied to the embedded rows in place on the stream, its weight named ``norm_tensor``."""
         self.vocab, self.width, self.name = vocab, width, name
+        self.tensor, self.norm, self.norm_tensor = tensor, norm, norm_tensor
         self.table: Optional[torch.Tensor] = None
 
+    def tensor_name(self, prefix: str) -> str:
+        return self.tensor if self.tensor is not None else f"{prefix}.{self.name}.weight"
+
     def param_specs(self, prefix: str) -> List[ParamSpec]:
-        return [ParamSpec(f"{prefix}.{self.name}.weight", (self.vocab, self.width), MATRIX)]
+        specs = [ParamSpec(self.tensor_name(prefix), (self.vocab, self.width), MATRIX)]
+        if self.norm is not None:
+            specs += self.norm.param_specs(self.norm_tensor)
+        return specs
 
     def load_params(self, state: Dict[str, torch.Tensor], prefix: str) -> None:
-        self.table = state[f"{prefix}.{self.name}.weight"]
+        self.table = state[self.tensor_name(prefix)]
+        if self.norm is not None:
+            self.norm.load_params(state, self.norm_tensor)
 
     def param_bytes(self) -> int:
-        return self.table.numel() * self.table.element_size()
+        return self.table.numel() * self.table.element_size() + (self.norm.param_bytes() if self.norm else 0)
 
     def forward(self, ctx: StepContext, x: torch.Tensor) -> None:
         ctx.ops.embed_rows(self.table, ctx.tokens, x)
+        if self.norm is not None:
+            self.norm.forward(ctx, x, x)
 
 
 class OutputHead(Part):

@@ -1,5 +1,8 @@
 """RMSNorm: y = (x * inv) * w, inv = 1 / sqrt(mean(x^2) + eps), no offset on the weight
-(src/kernels.cpp:264-271).  The statistic is always computed in 32-bit."""
+(src/kernels.cpp:264-271), and layer norm with a weight and no bias: y = (x - mean) / sqrt(var +
+eps) * w with var the mean of the squared deviations.  The statistics are always computed in
+32-bit.  ``suffix`` is what follows the prefix in the tensor's name (".weight" in Hugging Face
+checkpoints, nothing where the tensor carries the norm's own name)."""
 from __future__ import annotations
 
 from typing import Dict, List, Optional
@@ -13,16 +16,17 @@ from .base import Norm, StepContext, register_norm
 class RMSNorm(Norm):
     graph_safe = True  # kernels only: a step through this part can be captured
 
-    def __init__(self, width: int, eps: float):
+    def __init__(self, width: int, eps: float, suffix: str = ".weight"):
         self.width = width
         self.eps = float(eps)
+        self.suffix = suffix
         self.weight: Optional[torch.Tensor] = None
 
     def param_specs(self, prefix: str) -> List[ParamSpec]:
-        return [ParamSpec(prefix + ".weight", (self.width,), KEEP32, init="ones")]
+        return [ParamSpec(prefix + self.suffix, (self.width,), KEEP32, init="ones")]
 
     def load_params(self, state: Dict[str, torch.Tensor], prefix: str) -> None:
-        self.weight = state[prefix + ".weight"]
+        self.weight = state[prefix + self.suffix]
 
     def param_bytes(self) -> int:
         return self.weight.numel() * self.weight.element_size()
@@ -31,4 +35,21 @@ class RMSNorm(Norm):
         ctx.ops.rmsnorm(x, self.weight, self.eps, out, rows)
 
 
+class LayerNorm(RMSNorm):
+    """Mean and variance over the row; a weight, no bias.  ``out`` may be float32 (also ``x``
+    itself: the norm then works in place on the stream) or the activation type."""
+
+    def forward(self, ctx, x, out, rows=None) -> None:
+        ctx.ops.layernorm(x, self.weight, self.eps, out, rows)
+
+    def forward_pair(self, ctx, x, out, other: "LayerNorm", other_out) -> None:
+        """This norm and ``other`` of the same rows in one pass: they share mean and variance."""
+        if other.eps != self.eps or other.width != self.width:
+            self.forward(ctx, x, out)
+            other.forward(ctx, x, other_out)
+            return
+        ctx.ops.layernorm(x, self.weight, self.eps, out, None, other.weight, other_out)
+
+
 register_norm("rmsnorm", RMSNorm)
+register_norm("layernorm", LayerNorm)
