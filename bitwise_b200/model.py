@@ -93,6 +93,20 @@ class Model:
         return Model(decoder, dtype, device, ops)
 
     @staticmethod
+    def from_tensors(config, tensors, dtype: str = "bfloat16", device="cuda:0", ops=None) -> "Model":
+        """A model from tensors in memory (name -> CPU tensor), checked against what the
+        architecture declares like a checkpoint read from a folder."""
+        dtype = normalize_dtype(dtype)
+        arch = lookup_architecture(config.architectures[0])
+        decoder = arch.build(config)
+        ops = ops or _default_ops(dtype)
+        state = state_from_tensors(tensors, decoder.param_specs(), _TORCH_DTYPE[dtype], device,
+                                   ignorable=decoder.ignorable_tensor)
+        decoder.load_params(state, dtype, device)
+        decoder.prepare(ops)
+        return Model(decoder, dtype, device, ops)
+
+    @staticmethod
     def write_random_folder(folder: str, config, seed: int = 0, dtype: str = "float32", std: float = 0.02,
                             norm_jitter: float = 0.0) -> str:
         """Write ``config.json`` and ``model.safetensors`` of a random model (no device needed)."""
