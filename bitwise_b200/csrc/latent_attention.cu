@@ -12,6 +12,7 @@
 // single rows, with its merge. Scores, softmax weights, sums and rotations are float32 in both
 // precisions.
 #include "bw_act.cuh"
+#include "bw_mma.cuh"
 
 #include <math.h>
 
@@ -287,6 +288,184 @@ latent_attention_merge_kernel(const float* __restrict__ part, const int* __restr
   }
 }
 
+#if BW_ACT_BF16
+// ---------------------------------------------------------------------------------------
+// The same attention on the tensor cores (bfloat16 serving precision). A block takes up to 64
+// queries, (row, head) pairs of one query tile with the heads running fastest, and walks its
+// keys in tiles of 32 at the fixed absolute positions, two tiles in flight (cp.async). Four
+// warps own 16 queries each: scores S = Q K^T by mma.sync over rank + rot_dim (float32
+// accumulators: the scores are 32-bit), scaling, mask, running maximum and sum in float32, and
+// the weights enter the second product in two bfloat16 parts, p = hi + lo with lo = p - hi, so
+// that what multiplies the latents carries 16 bits of the float32 weight and not 8. The latents
+// of the tile (the first `rank` columns of the same shared-memory rows) are the second
+// product's right operand. With CS = 2 a second set of four warps repeats the scores and owns
+// the other half of the latent columns (a warp's accumulators are 16 x NT * 8 floats).
+// With `part` the block covers one span of keys and leaves (maximum, sum, unnormalised sum of
+// latents) per query for the merge; else it writes the finished rows.
+constexpr int kTcKeys = 32, kTcQueries = 64;
+
+template <int NT, int CS>
+__global__ void __launch_bounds__(128 * CS)
+latent_attention_tc_kernel(const act_t* __restrict__ q, int q_stride, const act_t* __restrict__ cache,
+                           const int* __restrict__ block_table, int max_blocks, const int* __restrict__ tile_seq,
+                           const int* __restrict__ tile_row0, const int* __restrict__ tile_rows,
+                           const int* __restrict__ seq_pos0, const int* __restrict__ seq_row0, act_t* out, int o_stride,
+                           float* __restrict__ part, int spans, int span, int heads, int hb, int rank, int rot_dim,
+                           int page, int window, float scale) {
+  bw::pdl_enter();
+  extern __shared__ __align__(16) unsigned char raw[];
+  const int dk = rank + rot_dim, rs = dk + 8;  // row stride in elements: an odd number of 16-byte pieces
+  __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(raw);
+  __nv_bfloat16* ks = qs + kTcQueries * rs;   // two tiles of kTcKeys rows
+  const int t = blockIdx.x, sp = blockIdx.z;
+  const int seq = tile_seq[t], row0 = tile_row0[t], rows = tile_rows[t];
+  const int h0 = blockIdx.y * hb;
+  const int nh = min(hb, heads - h0);
+  const int nq = rows * nh;
+  const int p0 = seq_pos0[seq] + (row0 - seq_row0[seq]);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int wq = warp & 3, cs = warp >> 2;
+  const int threads = 128 * CS, pieces = dk >> 3;
+  const int last = p0 + rows - 1;
+  const int first = window > 0 ? max(0, p0 - window + 1) : 0;
+  const int kbeg = max(sp * span, first / kTcKeys * kTcKeys), kend = min(last, (sp + 1) * span - 1);
+  const int tiles = kbeg <= kend ? (kend - kbeg) / kTcKeys + 1 : 0;
+  const int* bt = block_table + static_cast<size_t>(seq) * max_blocks;
+
+  for (int idx = tid; idx < kTcQueries * pieces; idx += threads) {
+    const int qi = idx / pieces, c = idx - qi * pieces;
+    const bool valid = qi < nq;
+    const act_t* src = valid ? q + static_cast<size_t>(row0 + qi / nh) * q_stride + (h0 + qi % nh) * dk + c * 8 : q;
+    bw::copy16_async(bw::smem_addr(qs + qi * rs + c * 8), src, valid);
+  }
+  auto load_keys_async = [&](int tile) {
+    __nv_bfloat16* dst = ks + (tile & 1) * kTcKeys * rs;
+    const int k0 = kbeg + tile * kTcKeys;
+    for (int idx = tid; idx < kTcKeys * pieces; idx += threads) {
+      const int kk = idx / pieces, c = idx - kk * pieces;
+      const int kp = k0 + kk;
+      const bool valid = kp <= kend;
+      const act_t* src = valid ? cache + (static_cast<size_t>(bt[kp / page]) * page + kp % page) * dk + c * 8 : cache;
+      bw::copy16_async(bw::smem_addr(dst + kk * rs + c * 8), src, valid);
+    }
+  };
+  if (tiles > 0) load_keys_async(0);
+  bw::copies_commit();
+
+  // the two query rows of this thread's accumulator fragments
+  const int qa = wq * 16 + (lane >> 2), qb = qa + 8;
+  const int pa = qa < nq ? p0 + qa / nh : -1, pb = qb < nq ? p0 + qb / nh : -1;
+  const int la = window > 0 ? max(0, pa - window + 1) : 0, lb = window > 0 ? max(0, pb - window + 1) : 0;
+  float ma = -INFINITY, mb = -INFINITY, suma = 0.0f, sumb = 0.0f;
+  float acc[NT][4];
+#pragma unroll
+  for (int i = 0; i < NT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.0f;
+
+  for (int tile = 0; tile < tiles; ++tile) {
+    if (tile + 1 < tiles) load_keys_async(tile + 1);
+    bw::copies_commit();
+    bw::copies_wait<1>();
+    __syncthreads();
+    const __nv_bfloat16* kt = ks + (tile & 1) * kTcKeys * rs;
+    const int k0 = kbeg + tile * kTcKeys;
+    float sc[4][4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.0f;
+    for (int kk = 0; kk < dk; kk += 16) {
+      uint32_t a[4], b0[4], b1[4];
+      bw::ldsm4(a, bw::smem_addr(qs + (wq * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * rs + kk + 8 * (lane >> 4)));
+      bw::ldsm4(b0, bw::smem_addr(kt + ((lane & 7) + 8 * (lane >> 4)) * rs + kk + 8 * ((lane >> 3) & 1)));
+      bw::ldsm4(b1, bw::smem_addr(kt + (16 + (lane & 7) + 8 * (lane >> 4)) * rs + kk + 8 * ((lane >> 3) & 1)));
+      bw::mma16816(sc[0], a, b0[0], b0[1]);
+      bw::mma16816(sc[1], a, b0[2], b0[3]);
+      bw::mma16816(sc[2], a, b1[0], b1[1]);
+      bw::mma16816(sc[3], a, b1[2], b1[3]);
+    }
+    float ta = -INFINITY, tb = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int kp = k0 + 8 * j + 2 * (lane & 3) + e;
+        const bool in_span = kp <= kend;
+        sc[j][e] = (in_span && kp <= pa && kp >= la) ? __fmul_rn(sc[j][e], scale) : -INFINITY;
+        sc[j][2 + e] = (in_span && kp <= pb && kp >= lb) ? __fmul_rn(sc[j][2 + e], scale) : -INFINITY;
+        ta = fmaxf(ta, sc[j][e]), tb = fmaxf(tb, sc[j][2 + e]);
+      }
+    ta = fmaxf(ta, __shfl_xor_sync(0xffffffffu, ta, 1)), ta = fmaxf(ta, __shfl_xor_sync(0xffffffffu, ta, 2));
+    tb = fmaxf(tb, __shfl_xor_sync(0xffffffffu, tb, 1)), tb = fmaxf(tb, __shfl_xor_sync(0xffffffffu, tb, 2));
+    const float na = fmaxf(ma, ta), nb = fmaxf(mb, tb);
+    const float base_a = na == -INFINITY ? 0.0f : na, base_b = nb == -INFINITY ? 0.0f : nb;
+    const float alpha_a = __expf(ma - base_a), alpha_b = __expf(mb - base_b);  // exp(-inf) = 0
+    ma = na, mb = nb;
+    float ra = 0.0f, rb = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        sc[j][e] = __expf(sc[j][e] - base_a), sc[j][2 + e] = __expf(sc[j][2 + e] - base_b);
+        ra += sc[j][e], rb += sc[j][2 + e];
+      }
+    suma = __fmaf_rn(suma, alpha_a, ra), sumb = __fmaf_rn(sumb, alpha_b, rb);
+#pragma unroll
+    for (int i = 0; i < NT; ++i) acc[i][0] *= alpha_a, acc[i][1] *= alpha_a, acc[i][2] *= alpha_b, acc[i][3] *= alpha_b;
+#pragma unroll
+    for (int k2 = 0; k2 < 2; ++k2) {
+      uint32_t hi[4], lo[4];
+#pragma unroll
+      for (int f = 0; f < 4; ++f) {
+        const float v0 = sc[2 * k2 + (f >> 1)][(f & 1) * 2], v1 = sc[2 * k2 + (f >> 1)][(f & 1) * 2 + 1];
+        const __nv_bfloat16 h0b = __float2bfloat16_rn(v0), h1b = __float2bfloat16_rn(v1);
+        hi[f] = bw::pack_bf16(v0, v1);
+        lo[f] = bw::pack_bf16(v0 - __bfloat162float(h0b), v1 - __bfloat162float(h1b));
+      }
+#pragma unroll
+      for (int np = 0; np < NT / 2; ++np) {
+        const int d0 = (cs * NT + 2 * np) * 8;
+        if (d0 < rank) {
+          uint32_t b[4];
+          bw::ldsm4_trans(b, bw::smem_addr(kt + (k2 * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * rs + d0 + 8 * (lane >> 4)));
+          bw::mma16816(acc[2 * np], hi, b[0], b[1]);
+          bw::mma16816(acc[2 * np], lo, b[0], b[1]);
+          bw::mma16816(acc[2 * np + 1], hi, b[2], b[3]);
+          bw::mma16816(acc[2 * np + 1], lo, b[2], b[3]);
+        }
+      }
+    }
+    __syncthreads();
+  }
+  bw::copies_wait<0>();
+  suma += __shfl_xor_sync(0xffffffffu, suma, 1), suma += __shfl_xor_sync(0xffffffffu, suma, 2);
+  sumb += __shfl_xor_sync(0xffffffffu, sumb, 1), sumb += __shfl_xor_sync(0xffffffffu, sumb, 2);
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int qi = half ? qb : qa;
+    if (qi >= nq) continue;
+    const int row = row0 + qi / nh, h = h0 + qi % nh;
+    const float m = half ? mb : ma, l = half ? sumb : suma;
+    if (part) {
+      float* rec = part + ((static_cast<size_t>(row) * heads + h) * spans + sp) * (rank + 2);
+      if (cs == 0 && (lane & 3) == 0) rec[0] = m, rec[1] = l;
+#pragma unroll
+      for (int i = 0; i < NT; ++i) {
+        const int d = (cs * NT + i) * 8 + 2 * (lane & 3);
+        if (d < rank) rec[2 + d] = acc[i][2 * half], rec[3 + d] = acc[i][2 * half + 1];
+      }
+    } else {
+      const float inv = __fdiv_rn(1.0f, l);
+      act_t* dst = out + static_cast<size_t>(row) * o_stride + h * rank;
+#pragma unroll
+      for (int i = 0; i < NT; ++i) {
+        const int d = (cs * NT + i) * 8 + 2 * (lane & 3);
+        if (d < rank) *reinterpret_cast<uint32_t*>(dst + d) = bw::pack_bf16(acc[i][2 * half] * inv, acc[i][2 * half + 1] * inv);
+      }
+    }
+  }
+}
+
+int g_force_plain_attention = 0;
+#endif
+
 size_t attention_smem(int rank, int rot_dim, int queries) {
   const int dk = rank + rot_dim;
   return (static_cast<size_t>(kKeys) * (dk + 1) + static_cast<size_t>(queries) * dk) * sizeof(float);
@@ -409,3 +588,72 @@ BW_API int BW_FN(latent_attention_split)(const act_t* q, int q_stride, const act
                  rank, out, o_stride);
   return bw::launch_status();
 }
+
+#if BW_ACT_BF16
+// Tests: 1 keeps attention on the plain kernels also where the tensor-core kernel would take
+// the shape. Returns the setting before.
+BW_API int BW_FN(latent_attention_force_plain)(int on) {
+  const int was = g_force_plain_attention;
+  g_force_plain_attention = on;
+  return was;
+}
+
+// Rows of one sequence per query tile for the tensor-core kernel, 0 where it does not take the
+// shape (the latent size a multiple of 8 up to 512, rank + rot_dim a multiple of 16, rows that
+// start on 16 bytes).
+BW_API int BW_FN(latent_attention_tc_tile_rows)(int heads, int rank, int rot_dim, int q_stride) {
+  const int dk = rank + rot_dim;
+  const size_t smem = static_cast<size_t>(kTcQueries + 2 * kTcKeys) * (dk + 8) * 2;
+  if (g_force_plain_attention || rank % 8 || dk % 16 || rank > 512 || q_stride % 8 || smem > 200 * 1024) return 0;
+  return heads >= kTcQueries ? 1 : kTcQueries / heads;
+}
+
+// Spans for steps of single rows: enough blocks for two per SM, spans of whole key tiles.
+BW_API int BW_FN(latent_attention_tc_spans)(int tiles, int heads, int max_keys, int* span_out) {
+  const int hb = heads < kTcQueries ? heads : kTcQueries;
+  const int blocks = tiles * ((heads + hb - 1) / hb);
+  int want = (2 * 148 + blocks - 1) / blocks;
+  if (want < 1) want = 1;
+  int span = (max_keys + want - 1) / want;
+  span = (span + 127) / 128 * 128;
+  *span_out = span;
+  return (max_keys + span - 1) / span;
+}
+
+// `scratch` null: query tiles of any height, finished rows. Else every tile is a single row, the
+// keys are split into spans (latent_attention_tc_spans) and the merge follows.
+BW_API int BW_FN(latent_attention_tc)(const act_t* q, int q_stride, const act_t* cache, const int* block_table,
+                                      int max_blocks, const int* tile_seq, const int* tile_row0, const int* tile_rows,
+                                      int tiles, const int* seq_pos0, const int* seq_row0, const int* pos, act_t* out,
+                                      int o_stride, int n, int heads, int rank, int rot_dim, int page, int window,
+                                      float scale, int max_keys, float* scratch, cudaStream_t stream) {
+  if (tiles <= 0) return 0;
+  if (!BW_FN(latent_attention_tc_tile_rows)(heads, rank, rot_dim, q_stride) || o_stride % 2) {
+    bw::set_error("latent attention: the tensor-core kernel does not take rank %d with rotated part %d", rank, rot_dim);
+    return -1;
+  }
+  const int dk = rank + rot_dim;
+  const int hb = heads < kTcQueries ? heads : kTcQueries;
+  const size_t smem = static_cast<size_t>(kTcQueries + 2 * kTcKeys) * (dk + 8) * 2;
+  int spans = 1, span = 1 << 30;
+  if (scratch) spans = BW_FN(latent_attention_tc_spans)(tiles, heads, max_keys, &span);
+  dim3 grid(tiles, (heads + hb - 1) / hb, spans);
+#define BW_LAUNCH(NT, CS)                                                                                          \
+  {                                                                                                                \
+    auto kernel = latent_attention_tc_kernel<NT, CS>;                                                              \
+    if (int rc = raise_smem(kernel, smem)) return rc;                                                              \
+    bw::launch_pdl(kernel, grid, dim3(128 * CS), smem, stream, q, q_stride, cache, block_table, max_blocks,        \
+                   tile_seq, tile_row0, tile_rows, seq_pos0, seq_row0, out, o_stride, scratch, spans, span, heads, \
+                   hb, rank, rot_dim, page, window, scale);                                                        \
+  }
+  if (rank <= 128) BW_LAUNCH(16, 1) else if (rank <= 256) BW_LAUNCH(32, 1) else BW_LAUNCH(32, 2)
+#undef BW_LAUNCH
+  if (int rc = bw::launch_status()) return rc;
+  if (scratch) {
+    bw::launch_pdl(latent_attention_merge_kernel, dim3(n, heads), dim3(128), 0, stream, scratch, pos, spans, span, heads,
+                   rank, out, o_stride);
+    return bw::launch_status();
+  }
+  return 0;
+}
+#endif

@@ -15,6 +15,7 @@
 //  * glu_clamped: y = g' sigmoid(alpha g') (u' + 1), g' = min(g, limit), u' = clamp(u, +-limit).
 //  * combine: x += d + sum_j weight_j * y[place of (row, j)], the sum in the order of choice.
 #include "bw_act.cuh"
+#include "bw_mma.cuh"
 
 #include <math.h>
 
@@ -232,6 +233,129 @@ grouped_linear_kernel(const act_t* __restrict__ x, int x_stride, int x_group_col
   }
 }
 
+#if BW_ACT_BF16
+// The same product on the tensor cores (bfloat16 in, float32 accumulators that walk k in
+// ascending steps of 16): tiles of 64 list entries x 64 outputs by four warps, k in slices of
+// 32 through a ring of three cp.async stages. For rows that start on 16 bytes (k, the row
+// strides and the groups' column offsets multiples of 8).
+constexpr int kMmaStages = 3, kMmaK = 32, kMmaRow = kMmaK + 8;  // 80-byte rows: ldmatrix without bank conflicts
+
+template <typename OutT>
+__global__ void __launch_bounds__(128)
+grouped_linear_mma_kernel(const act_t* __restrict__ x, int x_stride, int x_group_cols, const int* __restrict__ order,
+                          int order_div, const act_t* __restrict__ w, OutT* out, int o_stride, int o_group_cols,
+                          const int* __restrict__ group_off, const int* __restrict__ tile_prefix, int uniform_rows,
+                          int groups, int n, int k) {
+  bw::pdl_enter();
+  __shared__ __align__(16) __nv_bfloat16 xs[kMmaStages][kTile][kMmaRow];
+  __shared__ __align__(16) __nv_bfloat16 ws[kMmaStages][kTile][kMmaRow];
+  __shared__ int s_group;
+  int g, i0, i_end;
+  if (group_off) {
+    if (threadIdx.x == 0) {
+      int found = -1;
+      const int t = blockIdx.x;
+      if (t < tile_prefix[groups]) {
+        int lo = 0, hi = groups - 1;
+        while (lo < hi) {
+          const int mid = (lo + hi + 1) >> 1;
+          if (tile_prefix[mid] <= t) lo = mid; else hi = mid - 1;
+        }
+        found = lo;
+      }
+      s_group = found;
+    }
+    __syncthreads();
+    g = s_group;
+    if (g < 0) return;
+    i0 = group_off[g] + (blockIdx.x - tile_prefix[g]) * kTile;
+    i_end = group_off[g + 1];
+  } else {
+    const int tiles = (uniform_rows + kTile - 1) / kTile;
+    g = blockIdx.x / tiles;
+    i0 = (blockIdx.x - g * tiles) * kTile;
+    i_end = uniform_rows;
+  }
+  const int j0 = blockIdx.y * kTile;
+  const act_t* wg = w + static_cast<size_t>(g) * n * k;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int wm = (warp >> 1) * 32, wn = (warp & 1) * 32;
+  // a thread copies piece (tid % 4) of rows tid / 4 and tid / 4 + 32 of both tiles
+  const int piece = tid & 3, lr = tid >> 2;
+  const act_t* xrow[2];
+  const act_t* wrow[2];
+#pragma unroll
+  for (int q = 0; q < 2; ++q) {
+    const int i = i0 + lr + 32 * q;
+    xrow[q] = nullptr;
+    if (i < i_end) {
+      const int src = order ? order[i] / order_div : i;
+      xrow[q] = x + static_cast<size_t>(src) * x_stride + (group_off ? 0 : g * x_group_cols);
+    }
+    const int j = j0 + lr + 32 * q;
+    wrow[q] = j < n ? wg + static_cast<size_t>(j) * k : nullptr;
+  }
+  const int slices = (k + kMmaK - 1) / kMmaK;
+  auto load = [&](int slice) {
+    const int st = slice % kMmaStages, kk = slice * kMmaK + piece * 8;
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      const bool vx = xrow[q] && kk < k, vw = wrow[q] && kk < k;
+      bw::copy16_async(bw::smem_addr(&xs[st][lr + 32 * q][piece * 8]), vx ? xrow[q] + kk : x, vx);
+      bw::copy16_async(bw::smem_addr(&ws[st][lr + 32 * q][piece * 8]), vw ? wrow[q] + kk : w, vw);
+    }
+  };
+  float acc[2][4][4];
+#pragma unroll
+  for (int a = 0; a < 2; ++a)
+#pragma unroll
+    for (int b = 0; b < 4; ++b)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) acc[a][b][c] = 0.0f;
+#pragma unroll
+  for (int s = 0; s < kMmaStages - 1; ++s) {
+    if (s < slices) load(s);
+    bw::copies_commit();
+  }
+  for (int slice = 0; slice < slices; ++slice) {
+    bw::copies_wait<kMmaStages - 2>();
+    __syncthreads();
+    if (slice + kMmaStages - 1 < slices) load(slice + kMmaStages - 1);
+    bw::copies_commit();
+    const int st = slice % kMmaStages;
+#pragma unroll
+    for (int ks = 0; ks < kMmaK / 16; ++ks) {
+      uint32_t a[2][4], b[2][4];
+#pragma unroll
+      for (int mi = 0; mi < 2; ++mi)
+        bw::ldsm4(a[mi], bw::smem_addr(&xs[st][wm + mi * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)][ks * 16 + 8 * (lane >> 4)]));
+#pragma unroll
+      for (int np = 0; np < 2; ++np)
+        bw::ldsm4(b[np], bw::smem_addr(&ws[st][wn + np * 16 + (lane & 7) + 8 * (lane >> 4)][ks * 16 + 8 * ((lane >> 3) & 1)]));
+#pragma unroll
+      for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+        for (int ni = 0; ni < 4; ++ni) bw::mma16816(acc[mi][ni], a[mi], b[ni >> 1][(ni & 1) * 2], b[ni >> 1][(ni & 1) * 2 + 1]);
+    }
+  }
+  bw::copies_wait<0>();
+#pragma unroll
+  for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int i = i0 + wm + mi * 16 + (lane >> 2) + 8 * half;
+      if (i >= i_end) continue;
+      OutT* orow = out + static_cast<size_t>(i) * o_stride + (group_off ? 0 : g * o_group_cols);
+#pragma unroll
+      for (int ni = 0; ni < 4; ++ni) {
+        const int j = j0 + wn + ni * 8 + 2 * (lane & 3);
+        if (j < n) orow[j] = bw::from_f<OutT>(acc[mi][ni][2 * half]);
+        if (j + 1 < n) orow[j + 1] = bw::from_f<OutT>(acc[mi][ni][2 * half + 1]);
+      }
+    }
+}
+#endif
+
 // ---------------------------------------------------------------------------------------
 __global__ void glu_clamped_kernel(const act_t* __restrict__ gate_up, act_t* __restrict__ out, int inter, float limit,
                                    float alpha) {
@@ -286,6 +410,15 @@ BW_API int BW_FN(route)(const float* z, const float* correction, int n, int expe
 
 BW_API int BW_FN(grouped_tile_rows)() { return kTile; }
 
+// Tests: 1 keeps every grouped product on the plain kernel (one chain of fused multiply-adds per
+// output) also where the tensor-core kernel would take it. Returns the setting before.
+static int g_force_plain = 0;
+BW_API int BW_FN(grouped_force_plain)(int on) {
+  const int was = g_force_plain;
+  g_force_plain = on;
+  return was;
+}
+
 BW_API int BW_FN(group_rows)(const int* chosen, int pairs, int experts, int* group_off, int* tile_prefix, int* order,
                              int* place, cudaStream_t stream) {
   if (pairs <= 0) return 0;
@@ -318,6 +451,19 @@ BW_API int BW_FN(grouped_linear)(const act_t* x, int x_stride, int x_group_cols,
     bw::set_error("grouped_linear: %lld tiles exceed the grid", tiles);
     return -1;
   }
+#if BW_ACT_BF16
+  const bool aligned = k % 8 == 0 && x_stride % 8 == 0 && x_group_cols % 8 == 0 &&
+                       reinterpret_cast<uintptr_t>(x) % 16 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0;
+  if (aligned && !g_force_plain) {
+    if (out_is_f32)
+      bw::launch_pdl(grouped_linear_mma_kernel<float>, grid, dim3(128), 0, stream, x, x_stride, x_group_cols, order,
+                     order_div, w, static_cast<float*>(out), o_stride, o_group_cols, group_off, tile_prefix, rows, groups, n, k);
+    else
+      bw::launch_pdl(grouped_linear_mma_kernel<act_t>, grid, dim3(128), 0, stream, x, x_stride, x_group_cols, order,
+                     order_div, w, static_cast<act_t*>(out), o_stride, o_group_cols, group_off, tile_prefix, rows, groups, n, k);
+    return bw::launch_status();
+  }
+#endif
   if (out_is_f32)
     bw::launch_pdl(grouped_linear_kernel<float>, grid, dim3(256), 0, stream, x, x_stride, x_group_cols, order, order_div,
                    w, static_cast<float*>(out), o_stride, o_group_cols, group_off, tile_prefix, rows, groups, n, k);

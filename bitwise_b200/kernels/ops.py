@@ -690,6 +690,35 @@ class KernelOps:
         fn = getattr(self._parts_lib(), f"bw_{self.kind}_latent_attention_tile_rows")
         return int(fn(_c_int(heads)))
 
+    def latent_attention_tile_heights(self, heads: int, rank: int, rot_dim: int):
+        """The heights of query tiles that ``latent_attention`` may ask the step for: the plain
+        kernel's, and on the serving precision the tensor-core kernel's where it takes the shape."""
+        out = [self.latent_attention_tile_rows(heads)]
+        tc = self._latent_tc_rows(heads, rank, rot_dim)
+        if tc and tc not in out:
+            out.append(tc)
+        return out
+
+    def _latent_tc_rows(self, heads: int, rank: int, rot_dim: int) -> int:
+        if self.kind != "bf16":
+            return 0
+        fn = self._parts_lib().bw_bf16_latent_attention_tc_tile_rows
+        return int(fn(_c_int(heads), _c_int(rank), _c_int(rot_dim), _c_int(heads * (rank + rot_dim))))
+
+    def plain_parts(self, on: bool) -> None:
+        """Tests: keep latent attention and the grouped products on the plain kernels (one chain of
+        fused multiply-adds per output) also where the tensor-core kernels would take the shape."""
+        if self.kind == "bf16":
+            lib = self._parts_lib()
+            lib.bw_bf16_latent_attention_force_plain(_c_int(int(on)))
+            lib.bw_bf16_grouped_force_plain(_c_int(int(on)))
+
+    def _latent_scratch(self, floats: int, device) -> torch.Tensor:
+        if self._attn_scratch is None or self._attn_scratch.numel() < floats:
+            self._retired.append(self._attn_scratch)  # a captured graph may still point at the old one
+            self._attn_scratch = torch.empty(floats, dtype=torch.float32, device=device)
+        return self._attn_scratch
+
     def latent_attention(self, q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, out: torch.Tensor,
                          heads: int, rank: int, rot_dim: int, scale: float, batch, window: int = 0) -> None:
         """out[r, h] = sum_j softmax_j(q[r, h] . cache[j] * scale) cache[j][:rank] over the cached
@@ -705,6 +734,23 @@ class KernelOps:
         if q.shape[1] != heads * dk or cache.shape[2] != dk or tuple(out.shape) != (n, heads * rank):
             raise KernelError("latent_attention: shapes do not fit heads * (rank + rot_dim)")
         page = cache.shape[1]
+        tc_rows = self._latent_tc_rows(heads, rank, rot_dim)
+        if tc_rows and (not hasattr(batch, "tile_sets") or tc_rows in batch.tile_sets):
+            # the serving precision's tensor-core kernel; steps of single rows with long contexts
+            # spread every row's keys over several blocks and merge
+            t_seq, t_row0, t_rows, t_count = batch.query_tiles(tc_rows)
+            scratch, launches = None, 1
+            if t_count == n and batch.max_keys > 256:
+                span = _c_int(0)
+                spans = int(self._parts_lib().bw_bf16_latent_attention_tc_spans(_c_int(t_count), _c_int(heads),
+                                                                                _c_int(batch.max_keys), ctypes.byref(span)))
+                scratch, launches = self._latent_scratch(n * heads * spans * (rank + 2), q.device), 2
+            self._pcall("latent_attention_tc", _p(q), _c_int(q.shape[1]), _p(cache), _p(block_table),
+                        _c_int(block_table.shape[1]), _p(t_seq), _p(t_row0), _p(t_rows), _c_int(t_count),
+                        _p(batch.seq_pos0), _p(batch.seq_row0), _p(batch.pos), _p(out), _c_int(out.shape[1]), _c_int(n),
+                        _c_int(heads), _c_int(rank), _c_int(rot_dim), _c_int(page), _c_int(window), _c_float(scale),
+                        _c_int(batch.max_keys), _p(scratch), self._stream(), launches=launches)
+            return
         t_seq, t_row0, t_rows, t_count = batch.query_tiles(self.latent_attention_tile_rows(heads))
         if t_count == n and batch.max_keys > 256:
             # single rows with long contexts: spread every row's keys over many blocks
@@ -712,11 +758,7 @@ class KernelOps:
             span = _c_int(0)
             spans = int(getattr(lib, f"bw_{self.kind}_latent_attention_spans")(_c_int(n), _c_int(heads),
                                                                                _c_int(batch.max_keys), ctypes.byref(span)))
-            keys = (batch.max_keys + 2047) // 2048 * 2048  # sized so that it seldom grows
-            floats = n * heads * max(spans, (keys + span.value - 1) // span.value) * (rank + 2)
-            if self._attn_scratch is None or self._attn_scratch.numel() < floats:
-                self._retired.append(self._attn_scratch)  # a captured graph may still point at the old one
-                self._attn_scratch = torch.empty(floats, dtype=torch.float32, device=q.device)
+            self._latent_scratch(n * heads * spans * (rank + 2), q.device)
             self._pcall("latent_attention_split", _p(q), _c_int(q.shape[1]), _p(cache), _p(block_table),
                         _c_int(block_table.shape[1]), _p(batch.row_seq), _p(batch.pos), _p(out), _c_int(out.shape[1]),
                         _c_int(n), _c_int(heads), _c_int(rank), _c_int(rot_dim), _c_int(page), _c_int(window),

@@ -54,8 +54,8 @@ class LatentAttention(Mixer):
         return PagedLatentNeed(self.rank, self.rot_dim, self.window)
 
     def query_tile_rows(self, ops=None):
-        if ops is not None and hasattr(ops, "latent_attention_tile_rows"):
-            return [ops.latent_attention_tile_rows(self.heads)]
+        if ops is not None and hasattr(ops, "latent_attention_tile_heights"):
+            return list(ops.latent_attention_tile_heights(self.heads, self.rank, self.rot_dim))
         return [max(1, 32 // self.heads)]
 
     def param_specs(self, prefix: str) -> List[ParamSpec]:

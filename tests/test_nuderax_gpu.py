@@ -42,27 +42,31 @@ def close(got, want, dtype, what="", factor=1.0):
 class Batch:
     """What the attention kernels read of a step: rows of sequences, their positions, tiles."""
 
-    def __init__(self, seqs, tile_rows, granule=1):
+    def __init__(self, seqs, granule=1):
         # seqs: list of (first position, rows); one block-table row each
-        pos, row_seq, t_seq, t_row0, t_rows, seq_pos0, seq_row0 = [], [], [], [], [], [], []
+        pos, row_seq, seq_pos0, seq_row0 = [], [], [], []
         r = 0
         for s, (p0, cnt) in enumerate(seqs):
             seq_pos0.append(p0), seq_row0.append(r)
             pos += list(range(p0, p0 + cnt))
             row_seq += [s] * cnt
-            for a in range(0, cnt, tile_rows):
-                t_seq.append(s), t_row0.append(r + a), t_rows.append(min(tile_rows, cnt - a))
             r += cnt
-        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
-        self.n = r
-        self.pos, self.row_seq, self.seq_pos0, self.seq_row0 = i32(pos), i32(row_seq), i32(seq_pos0), i32(seq_row0 + [r])
-        self._tiles = (i32(t_seq), i32(t_row0), i32(t_rows), len(t_seq))
+        self.i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+        self.n, self.seqs = r, seqs
+        self.pos, self.row_seq = self.i32(pos), self.i32(row_seq)
+        self.seq_pos0, self.seq_row0 = self.i32(seq_pos0), self.i32(seq_row0 + [r])
         self.max_keys = (max(pos) + 1 + granule - 1) // granule * granule
         self.host_pos = pos
         self.host_row_seq = row_seq
 
-    def query_tiles(self, rows):
-        return self._tiles
+    def query_tiles(self, tile_rows):
+        t_seq, t_row0, t_rows = [], [], []
+        r = 0
+        for s, (p0, cnt) in enumerate(self.seqs):
+            for a in range(0, cnt, tile_rows):
+                t_seq.append(s), t_row0.append(r + a), t_rows.append(min(tile_rows, cnt - a))
+            r += cnt
+        return self.i32(t_seq), self.i32(t_row0), self.i32(t_rows), len(t_seq)
 
 
 # ---------------------------------------------------------------------------------------------
@@ -129,7 +133,21 @@ def test_latent_store_and_query_rotation(dtype, rank, rot_dim, dims):
     assert not bool(got[:, :, :rank].any()), "the folded part was touched"
 
 
-def _attention_case(dtype, heads, rank, rot_dim, seqs, spike=None, window=0, force_split=False, page=16):
+def _attention_case(dtype, *args, **kw):
+    """On the serving precision: once on the tensor-core kernel (where it takes the shape), once
+    on the plain one."""
+    out = _attention_case_once(dtype, *args, **kw)
+    if dtype == "bfloat16":
+        ops = ops_of(dtype)
+        ops.plain_parts(True)
+        try:
+            out = min(out, _attention_case_once(dtype, *args, **kw)) if out is not None else _attention_case_once(dtype, *args, **kw)
+        finally:
+            ops.plain_parts(False)
+    return out
+
+
+def _attention_case_once(dtype, heads, rank, rot_dim, seqs, spike=None, window=0, force_split=False, page=16):
     """Random queries and a random cache through the kernel and through plain softmax attention.
     ``spike``: (sequence, row, key position): that query and key get a large common component, so
     that one key far back carries nearly all of the weight."""
@@ -152,8 +170,7 @@ def _attention_case(dtype, heads, rank, rot_dim, seqs, spike=None, window=0, for
             chunk = k[b * page:(b + 1) * page]
             cache[perm[at], :chunk.shape[0]] = chunk
             at += 1
-    tile_rows = ops.latent_attention_tile_rows(heads)
-    batch = Batch(seqs, tile_rows, granule=256 if force_split else 1)
+    batch = Batch(seqs, granule=256 if force_split else 1)
     if force_split:
         assert batch.n == len(seqs) and batch.max_keys > 256
     q = torch.randn(batch.n, heads, dk, generator=g).to(act(dtype))
@@ -184,7 +201,8 @@ def _attention_case(dtype, heads, rank, rot_dim, seqs, spike=None, window=0, for
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("heads,rank,rot_dim", [(3, 40, 8), (1, 33, 6), (40, 136, 4), (8, 96, 16), (5, 300, 20)])
+@pytest.mark.parametrize("heads,rank,rot_dim", [(3, 40, 8), (1, 33, 6), (40, 136, 4), (8, 96, 16), (5, 300, 20),
+                                                (70, 64, 16), (6, 264, 24), (2, 512, 64)])
 def test_latent_attention_tiles(dtype, heads, rank, rot_dim):
     # portions that begin in the middle of a page and of a key tile, single rows beside them,
     # the first positions of a sequence, lengths at and around multiples of 16 and 32
@@ -201,7 +219,7 @@ def test_latent_attention_far_key(dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("heads,rank,rot_dim", [(3, 40, 8), (20, 136, 4)])
+@pytest.mark.parametrize("heads,rank,rot_dim", [(3, 40, 8), (20, 136, 4), (70, 64, 16), (2, 512, 64)])
 def test_latent_attention_split_over_keys(dtype, heads, rank, rot_dim):
     # single rows with contexts past 256 keys take the kernel that spreads a row's keys over
     # blocks; contexts of one key, of a whole number of spans, and one key more
@@ -235,11 +253,21 @@ def test_route(experts, groups, keep, top):
     close(weights, want_w, "float32", "weights")
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_grouped_products_activation_and_combination(dtype):
+@pytest.mark.parametrize("dtype,width,inner,plain", [("float32", 50, 19, False), ("bfloat16", 50, 19, False),
+                                                     ("bfloat16", 72, 40, False), ("bfloat16", 72, 40, True)])
+def test_grouped_products_activation_and_combination(dtype, width, inner, plain):
+    # widths that are multiples of 8 take the tensor-core kernel on the serving precision
     ops = ops_of(dtype)
+    ops.plain_parts(plain)
+    try:
+        _grouped_case(ops, dtype, width, inner)
+    finally:
+        ops.plain_parts(False)
+
+
+def _grouped_case(ops, dtype, width, inner):
     g = torch.Generator().manual_seed(5)
-    n, top, experts, width, inner = 150, 3, 7, 50, 19      # expert 4 is never chosen, others get unequal shares
+    n, top, experts = 150, 3, 7                              # expert 4 is never chosen, others get unequal shares
     chosen = torch.stack([torch.tensor([0, 1, 2, 3, 5, 6])[torch.randperm(6, generator=g)[:top]] for _ in range(n)])
     chosen[:100, 0] = 5                                     # more than one tile of rows for one expert
     chosen[:100, 1:] = torch.tensor([0, 1])
@@ -281,8 +309,8 @@ def test_grouped_products_activation_and_combination(dtype):
     ops.combine(stream, d, y, place, weights, top)
     close(stream, want, "float32", "combination")
     # one product per head: every group takes every row and its own columns
-    heads, k, m = 5, 11, 13
-    xs = torch.randn(70, heads * k + 3, generator=g).to(act(dtype))
+    heads, k, m = (5, 11, 13) if width == 50 else (5, 24, 13)
+    xs = torch.randn(70, heads * k + (3 if width == 50 else 8), generator=g).to(act(dtype))
     wh = torch.randn(heads, m, k, generator=g).to(act(dtype))
     out = torch.zeros(70, heads * m + 2, dtype=act(dtype), device=DEV)
     ops.grouped_linear(xs.to(DEV)[:, :], wh.to(DEV), out, 70, x_group_cols=k, o_group_cols=m)
