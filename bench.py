@@ -290,6 +290,223 @@ def run_e2e(model, batch, ctx, steps, warmup, page, fingerprint=True):
     return made / dt, h2d, d2h
 
 
+# ---- the Nuderax design beside Llama at equal size (--compare nuderax) -------------------------
+NUDERAX_SIZES = {
+    # width, layers run, heads, dim, rot_dim, vdim, kv_rank, q_rank, experts, groups, keep, top, ff, shared ff, vocab
+    "small": dict(width=1024, layers=4, heads=8, dim=64, rot_dim=32, vdim=64, kv_rank=256, q_rank=512, experts=16,
+                  groups=4, keep=2, top=2, ff=512, shared_ff=1024, vocab=32768),
+    "medium": dict(width=2048, layers=4, heads=16, dim=128, rot_dim=64, vdim=128, kv_rank=512, q_rank=1024, experts=64,
+                   groups=8, keep=4, top=6, ff=1408, shared_ff=2816, vocab=32768),
+}
+
+
+def nuderax_config(z):
+    from bitwise_b200.config import LatentMixerConfig, NuderaxConfig, NuderaxLayerConfig, RoutedMlpConfig
+    layers = []
+    for i in range(z["layers"]):
+        kind = "latent_attention_2" if i % 2 == 0 else "latent_attention"
+        m = LatentMixerConfig(kind, z["heads"], z["dim"], z["rot_dim"], z["vdim"], z["kv_rank"],
+                              (z["dim"] + z["rot_dim"]) ** -0.5, 10000.0, z["rot_dim"],
+                              z["q_rank"] if kind == "latent_attention_2" else None, None)
+        f = RoutedMlpConfig(z["experts"], z["top"], 1.0, z["groups"], z["keep"], z["ff"], 7.0, z["shared_ff"], 7.0)
+        layers.append(NuderaxLayerConfig(m, f))
+    return NuderaxConfig(vocab=z["vocab"], width=z["width"], eps=1e-5, layers=tuple(layers))
+
+
+def llama_twin(z):
+    """Llama with the same width, layers, heads and vocabulary, a head of dim + rot_dim, and the
+    feed-forward width a token of the routed model is multiplied with (top experts and the shared one)."""
+    from bitwise_b200 import LlamaConfig
+    return LlamaConfig(vocab_size=z["vocab"], hidden_size=z["width"], num_hidden_layers=z["layers"],
+                       num_attention_heads=z["heads"], num_key_value_heads=z["heads"], head_dim=z["vdim"],
+                       intermediate_size=(z["top"] * z["ff"] + z["shared_ff"]) // 64 * 64, rope_theta=10000.0,
+                       rms_norm_eps=1e-5, tie_word_embeddings=True, max_position_embeddings=8192)
+
+
+class KernelBatch:
+    """A step's index arrays for timing a kernel alone: ``seqs`` = [(first position, rows)]."""
+
+    def __init__(self, seqs, heights, device, granule=256):
+        import torch
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=device)
+        pos, row_seq, p0s, r0s = [], [], [], []
+        r = 0
+        for s, (p0, cnt) in enumerate(seqs):
+            p0s.append(p0), r0s.append(r)
+            pos += list(range(p0, p0 + cnt))
+            row_seq += [s] * cnt
+            r += cnt
+        self.n, self.num_seqs = r, len(seqs)
+        self.pos, self.row_seq, self.seq_pos0, self.seq_row0 = i32(pos), i32(row_seq), i32(p0s), i32(r0s + [r])
+        self.max_keys = (max(pos) + 1 + granule - 1) // granule * granule
+        self.tile_sets = {}
+        for h in heights:
+            listed = []
+            for s, (p0, cnt) in enumerate(seqs):
+                for a in range(0, cnt, h):
+                    rows = min(h, cnt - a)
+                    listed.append((-(p0 + a + rows), s, r0s[s] + a, rows))
+            listed.sort()
+            self.tile_sets[h] = (i32([x[1] for x in listed]), i32([x[2] for x in listed]), i32([x[3] for x in listed]),
+                                 len(listed))
+
+    def query_tiles(self, h):
+        return self.tile_sets[h]
+
+
+def timed(fn, reps=7, flush=None):
+    """Median device time in ms of ``fn`` (CUDA events on the launching stream); ``flush`` is
+    written before every repetition so that nothing of the last one stays in L2."""
+    import torch
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    times = []
+    for i in range(reps + 3):
+        if flush is not None:
+            flush.zero_()
+        torch.cuda.synchronize()
+        ev0.record()
+        fn()
+        ev1.record()
+        torch.cuda.synchronize()
+        if i >= 3:
+            times.append(ev0.elapsed_time(ev1))
+    return sorted(times)[len(times) // 2]
+
+
+def kernel_table(z, pk, page=16):
+    """Every new kernel alone at the size's shapes beside the like kernel of the Llama twin:
+    milliseconds and the fraction of its roofline (measured copy bandwidth or bf16 peak)."""
+    import torch
+    from bitwise_b200.kernels.ops import get_ops
+    ops = get_ops("bfloat16")
+    dev, bf = "cuda:0", torch.bfloat16
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    H, rank, rot, dim, vdim, width = z["heads"], z["kv_rank"], z["rot_dim"], z["dim"], z["vdim"], z["width"]
+    dk = rank + rot
+    hd = vdim
+    out = {}
+
+    def frac_flops(flops, ms):
+        return round(flops / (ms / 1e3) / 1e12 / pk["bf16_tflops"], 4)
+
+    def frac_bytes(nbytes, ms):
+        return round(nbytes / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 4)
+
+    def put(name, ms, frac, twin_ms, twin_frac, bound):
+        out[name] = {"ms": round(ms, 4), "frac": frac, "twin_ms": round(twin_ms, 4), "twin_frac": twin_frac, "bound": bound,
+                     "gap_ratio": round(twin_frac / frac, 2) if frac else None}
+
+    for label, seqs in (("prefill_2048", [(0, 2048)]), ("decode_b8_ctx2048", [(2047, 1)] * 8)):
+        keys = max(p0 + c for p0, c in seqs)
+        blocks = (keys + page - 1) // page
+        nseq = len(seqs)
+        table = torch.arange(nseq * blocks, dtype=torch.int32, device=dev).reshape(nseq, blocks)
+        heights = set(ops.latent_attention_tile_heights(H, rank, rot)) | set(ops.attention_tile_heights(H, H, hd))
+        b = KernelBatch(seqs, sorted(heights), dev)
+        n = b.n
+        pairs = sum(c * p0 + c * (c + 1) // 2 for p0, c in seqs)
+        # latent attention
+        cache = torch.randn(nseq * blocks + 1, page, dk, device=dev).to(bf)
+        q = torch.randn(n, H * dk, device=dev).to(bf)
+        o = torch.empty(n, H * rank, dtype=bf, device=dev)
+        ms = timed(lambda: ops.latent_attention(q, cache, table, o, H, rank, rot, dk ** -0.5, b), flush=flush)
+        # the Llama twin's attention
+        kc = torch.randn(nseq * blocks + 1, H, page, hd, device=dev).to(bf)
+        vc = torch.randn(nseq * blocks + 1, H, page, hd, device=dev).to(bf)
+        qkv = torch.randn(n, 3 * H * hd, device=dev).to(bf)
+        o2 = torch.empty(n, H * hd, dtype=bf, device=dev)
+        tms = timed(lambda: ops.attention(qkv, kc, vc, table, b.row_seq, b.pos, o2, H, H, hd, 0, b.max_keys, hd ** -0.5,
+                                          batch=b), flush=flush)
+        if n > nseq:
+            put(f"attention_{label}", ms, frac_flops(2.0 * H * (dk + rank) * pairs, ms), tms,
+                frac_flops(4.0 * H * hd * pairs, tms), "bf16 peak")
+        else:
+            put(f"attention_{label}", ms, frac_bytes(nseq * keys * dk * 2, ms), tms, frac_bytes(nseq * keys * 2 * H * hd * 2, tms),
+                "copy bandwidth")
+        # the experts' products against the twin's dense ones
+        E, top, ff = z["experts"], z["top"], z["ff"]
+        inter = (top * ff + z["shared_ff"]) // 64 * 64
+        x = torch.randn(n, width, device=dev).to(bf)
+        chosen = torch.stack([torch.randperm(E, device=dev)[:top] for _ in range(n)]).to(torch.int32)
+        lists = torch.empty(2, E + 1, dtype=torch.int32, device=dev)
+        order = torch.empty(n * top, dtype=torch.int32, device=dev)
+        place = torch.empty(n * top, dtype=torch.int32, device=dev)
+        ops.group_rows(chosen, E, lists[0], lists[1], order, place)
+        w1 = (torch.randn(E, 2 * ff, width, device=dev) * 0.02).to(bf)
+        w2 = (torch.randn(E, width, ff, device=dev) * 0.02).to(bf)
+        gu = torch.empty(n * top, 2 * ff, dtype=bf, device=dev)
+        hh = torch.randn(n * top, ff, device=dev).to(bf)
+        y = torch.empty(n * top, width, dtype=torch.float32, device=dev)
+        grouped = (lists[0], lists[1], order)
+        ms1 = timed(lambda: ops.grouped_linear(x, w1, gu, n * top, lists=grouped, order_div=top), flush=flush)
+        ms2 = timed(lambda: ops.grouped_linear(hh, w2, y, n * top, lists=grouped, gather=False), flush=flush)
+        wd1 = (torch.randn(2 * inter, width, device=dev) * 0.02).to(bf)
+        wd2 = (torch.randn(width, inter, device=dev) * 0.02).to(bf)
+        g2 = torch.empty(n, 2 * inter, dtype=bf, device=dev)
+        h2 = torch.randn(n, inter, device=dev).to(bf)
+        y2 = torch.zeros(n, width, dtype=torch.float32, device=dev)
+        t1 = timed(lambda: ops.linear(x, wd1, g2), flush=flush)
+        t2 = timed(lambda: ops.linear(h2, wd2, y2, residual=y2), flush=flush)
+        used = min(E, n * top) if n * top < 4 * E else E  # experts whose weights a step reads (about)
+        if n > nseq:
+            put(f"experts_gate_up_{label}", ms1, frac_flops(2.0 * n * top * 2 * ff * width, ms1), t1,
+                frac_flops(2.0 * n * 2 * inter * width, t1), "bf16 peak")
+            put(f"experts_down_{label}", ms2, frac_flops(2.0 * n * top * ff * width, ms2), t2,
+                frac_flops(2.0 * n * inter * width, t2), "bf16 peak")
+        else:
+            used = int(torch.unique(chosen).numel())
+            put(f"experts_gate_up_{label}", ms1, frac_bytes(used * 2 * ff * width * 2, ms1), t1,
+                frac_bytes(2 * inter * width * 2, t1), "copy bandwidth")
+            put(f"experts_down_{label}", ms2, frac_bytes(used * ff * width * 2, ms2), t2, frac_bytes(inter * width * 2, t2),
+                "copy bandwidth")
+        # the products per head around attention (no twin: Llama has none), the norms, the routing
+        qh = torch.randn(n, H * (dim + rot), device=dev).to(bf)
+        wk = (torch.randn(H, rank, dim, device=dev) * 0.05).to(bf)
+        qf = torch.empty(n, H * dk, dtype=bf, device=dev)
+        ms = timed(lambda: ops.grouped_linear(qh, wk, qf, n, x_group_cols=dim + rot, o_group_cols=dk), flush=flush)
+        fl, by = 2.0 * n * H * rank * dim, (H * rank * dim + n * H * (dim + dk)) * 2
+        out[f"fold_keys_into_queries_{label}"] = {"ms": round(ms, 4), "frac": max(frac_flops(fl, ms), frac_bytes(by, ms)),
+                                                  "bound": "the larger of both fractions"}
+        stream = torch.randn(n, width, device=dev)
+        wn = torch.ones(width, device=dev)
+        a1, a2 = torch.empty(n, width, dtype=bf, device=dev), torch.empty(n, width, dtype=bf, device=dev)
+        ms = timed(lambda: ops.layernorm(stream, wn, 1e-5, a1, None, wn, a2), flush=flush)
+        tms = timed(lambda: ops.rmsnorm(stream, wn, 1e-5, a1), flush=flush)
+        put(f"norm_{label}", ms, frac_bytes(n * width * 8, ms), tms, frac_bytes(n * width * 6, tms), "copy bandwidth")
+        zl = torch.randn(n, E, device=dev)
+        wts = torch.empty(n, top, dtype=torch.float32, device=dev)
+        ms = timed(lambda: (ops.route(zl, None, z["groups"], z["keep"], top, 1.0, chosen, wts),
+                            ops.group_rows(chosen, E, lists[0], lists[1], order, place)), flush=flush)
+        out[f"route_and_group_{label}"] = {"ms": round(ms, 4), "bound": "latency (two small kernels)"}
+        del cache, kc, vc, w1, w2, wd1, wd2
+        torch.cuda.empty_cache()
+    return out
+
+
+def compare_nuderax(args, pk):
+    import torch
+    from bitwise_b200 import Model
+    z = NUDERAX_SIZES[args.size]
+    line = {"metric": f"Nuderax beside Llama at equal size ({args.size}): prefill of 2,048 tokens and decode at batch "
+                      f"{args.batch}, {args.ctx or 2048:,}-token contexts", "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16",
+            "data": "synthetic: random N(0,0.02) weights, prompt ids uniform over the vocabulary", "size": z,
+            "peaks": "of " + pk["source"], "l2": "whole models: weights and cache exceed L2; kernels alone: L2 flushed "
+            "before every repetition"}
+    ctx = args.ctx or 2048
+    for name, cfg in (("nuderax", nuderax_config(z)), ("llama_twin", llama_twin(z))):
+        model = Model.random(cfg, seed=0, dtype="bfloat16", device="cuda:0", fast=True)
+        with ClockSampler() as clocks:
+            ms, launches = run_decode(model, args.batch, ctx, args.steps, max(3, args.warmup), args.page)
+        pms = run_prefill(model, 2048, reps=5, warmup=3, page=args.page)
+        line[name] = {"decode_tok_s": round(args.batch / (ms / 1e3), 1), "decode_ms_per_step": round(ms, 4),
+                      "prefill_tok_s": round(2048 / (pms / 1e3), 1), "prefill_ms": round(pms, 3),
+                      "weight_bytes": model.weight_bytes, "gpu_launches": launches, "clocks": clocks.summary()}
+        del model
+        torch.cuda.empty_cache()
+    line["kernels"] = kernel_table(z, pk, args.page)
+    return line
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -308,6 +525,9 @@ def main():
     ap.add_argument("--page", type=int, default=16)
     ap.add_argument("--skip-points", action="store_true", help="only the headline decode (for profiling runs)")
     ap.add_argument("--skip-prefill", action="store_true")
+    ap.add_argument("--compare", default="", choices=["", "nuderax"],
+                    help="instead of the headline: this design beside the Llama architecture at equal size")
+    ap.add_argument("--size", default="small", choices=sorted(NUDERAX_SIZES), help="layer sizes for --compare")
     args = ap.parse_args()
 
     if args.gpus != 1:
@@ -321,6 +541,9 @@ def main():
     import torch
     from bitwise_b200 import Model
     pk = peaks()
+    if args.compare == "nuderax":
+        print(json.dumps(compare_nuderax(args, pk)))
+        return 0
     title, full_layers, _, shape_ctx = SHAPES[args.shape]
     args.layers = args.layers or full_layers
     args.ctx = args.ctx or shape_ctx

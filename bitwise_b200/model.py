@@ -19,7 +19,7 @@ import torch
 from .cache.storage import build_cache
 from .config.registry import architecture_of, config_from_folder, lookup_architecture
 from .engine.step import StepEntry, Stepper
-from .weights.loader import load_state, state_from_tensors
+from .weights.loader import KEEP32, load_state, state_from_tensors
 from .weights.random_init import random_tensors, write_model_folder
 
 _TORCH_DTYPE = {"float32": torch.float32, "bfloat16": torch.bfloat16}
@@ -83,7 +83,7 @@ class Model:
                 else:
                     t = torch.empty(s.shape, dtype=torch.float32, device=device)
                     t.normal_(0.0, std, generator=gen)
-                    state[s.name] = t.to(tdt)
+                    state[s.name] = t if s.kind == KEEP32 else t.to(tdt)
         else:
             tensors = random_tensors(specs, seed, torch.float32 if dtype == "float32" else torch.bfloat16,
                                      std, norm_jitter)
