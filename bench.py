@@ -428,17 +428,18 @@ def kernel_table(z, pk, page=16):
         inter = (top * ff + z["shared_ff"]) // 64 * 64
         x = torch.randn(n, width, device=dev).to(bf)
         chosen = torch.stack([torch.randperm(E, device=dev)[:top] for _ in range(n)]).to(torch.int32)
-        lists = torch.empty(2, E + 1, dtype=torch.int32, device=dev)
+        lists = torch.empty(3, E + 1, dtype=torch.int32, device=dev)
         order = torch.empty(n * top, dtype=torch.int32, device=dev)
         place = torch.empty(n * top, dtype=torch.int32, device=dev)
-        ops.group_rows(chosen, E, lists[0], lists[1], order, place)
+        ops.group_rows(chosen, E, lists[0], lists[1:3], order, place)
         w1 = (torch.randn(E, 2 * ff, width, device=dev) * 0.02).to(bf)
         w2 = (torch.randn(E, width, ff, device=dev) * 0.02).to(bf)
         gu = torch.empty(n * top, 2 * ff, dtype=bf, device=dev)
         hh = torch.randn(n * top, ff, device=dev).to(bf)
         y = torch.empty(n * top, width, dtype=torch.float32, device=dev)
-        grouped = (lists[0], lists[1], order)
-        ms1 = timed(lambda: ops.grouped_linear(x, w1, gu, n * top, lists=grouped, order_div=top), flush=flush)
+        grouped = (lists[0], lists[1:3], order)
+        xs = torch.empty(n * top, width, dtype=bf, device=dev)
+        ms1 = timed(lambda: ops.grouped_linear(x, w1, gu, n * top, lists=grouped, order_div=top, sorted_x=xs), flush=flush)
         ms2 = timed(lambda: ops.grouped_linear(hh, w2, y, n * top, lists=grouped, gather=False), flush=flush)
         wd1 = (torch.randn(2 * inter, width, device=dev) * 0.02).to(bf)
         wd2 = (torch.randn(width, inter, device=dev) * 0.02).to(bf)
@@ -476,7 +477,7 @@ def kernel_table(z, pk, page=16):
         zl = torch.randn(n, E, device=dev)
         wts = torch.empty(n, top, dtype=torch.float32, device=dev)
         ms = timed(lambda: (ops.route(zl, None, z["groups"], z["keep"], top, 1.0, chosen, wts),
-                            ops.group_rows(chosen, E, lists[0], lists[1], order, place)), flush=flush)
+                            ops.group_rows(chosen, E, lists[0], lists[1:3], order, place)), flush=flush)
         out[f"route_and_group_{label}"] = {"ms": round(ms, 4), "bound": "latency (two small kernels)"}
         del cache, kc, vc, w1, w2, wd1, wd2
         torch.cuda.empty_cache()

@@ -326,10 +326,26 @@ __global__ void reduce_swiglu_kernel(const float* __restrict__ partials, int num
 // stay in registers.
 //
 // PAIR (with WIDE, whole mode): two blocks of a cluster share a 256 x 256 tile, see above.
-template <bool SPLIT, int A_ROWS, int EPI, bool WIDE, bool PAIR>
+//
+// GROUPED (whole mode): one product per group over lists of rows. x holds the rows group by group
+// (group g owns rows group_off[g] .. group_off[g + 1] - 1), W is [groups * N][K], y row i is x row
+// i times the transposed weights of i's group. A work item is a tile of 128 rows of ONE group
+// (tile_prefix[g]: tiles before group g) and a block of columns; the loader takes the group's
+// rows of W, the epilogue stores the rows up to the group's end. Rows that a tile reads beyond
+// its group are the next group's or zeros, and their results are never stored. The lists are
+// written by a kernel of the same step, so every role waits for it before it reads them.
+struct GroupItems {
+  const int* group_off;
+  const int* tile_prefix;
+  int groups;
+};
+
+template <bool SPLIT, int A_ROWS, int EPI, bool WIDE, bool PAIR, bool GROUPED = false>
 __global__ void __launch_bounds__(WIDE ? 384 : 192, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, void* Y,
-               int y_is_f32, const float* residual, int M, int N, int K, int* error_flag, float* partials, int bn) {
+               int y_is_f32, const float* residual, int M, int N, int K, int* error_flag, float* partials, int bn,
+               GroupItems gi) {
+  static_assert(!GROUPED || (!SPLIT && !PAIR && A_ROWS == BM && EPI != 1), "grouped products run whole, single-block tiles");
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // the swizzled tiles want 1024-byte alignment
   unsigned char* tiles = bw::smem_align_1024(smem_raw);
@@ -361,9 +377,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   // t % m_blocks and columns of block t / m_blocks, all its chunks (blocks that run at the same
   // time share W tiles through L2). Split mode (one block of rows): item t is chunk
   // t % num_chunks of the output tile with columns of block t / num_chunks.
-  const int out_tiles = SPLIT ? n_blocks * num_chunks : m_blocks * n_blocks;
+  int out_tiles = SPLIT ? n_blocks * num_chunks : m_blocks * n_blocks;
+  int row_tiles = m_blocks;  // grouped: the tiles of all groups together, known once the lists are written
+  auto read_lists = [&]() {
+    if (GROUPED) {
+      bw::pdl_wait();
+      row_tiles = gi.tile_prefix[gi.groups];
+      out_tiles = row_tiles * n_blocks;
+    }
+  };
+  // grouped: the group of row tile mt (the last one whose first tile is at or before it), the
+  // tile's first row and the group's end
+  auto group_tile = [&](int t, int& m0, int& m_end, int& g) {
+    const int mt = t % row_tiles;
+    int lo = 0, hi = gi.groups - 1;
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (gi.tile_prefix[mid] <= mt) lo = mid; else hi = mid - 1;
+    }
+    g = lo;
+    m0 = gi.group_off[lo] + (mt - gi.tile_prefix[lo]) * BM;
+    m_end = gi.group_off[lo + 1];
+  };
   auto item_m0 = [&](int t) { return SPLIT ? 0 : (t % m_blocks) * BMT + static_cast<int>(rank) * BM; };
-  auto item_n0 = [&](int t) { return SPLIT ? (t / num_chunks) * bt : (t / m_blocks) * bt; };
+  auto item_n0 = [&](int t) { return SPLIT ? (t / num_chunks) * bt : (t / (GROUPED ? row_tiles : m_blocks)) * bt; };
   auto item_c0 = [&](int t) { return SPLIT ? t % num_chunks : 0; };
   auto item_c1 = [&](int t) { return SPLIT ? t % num_chunks + 1 : num_chunks; };
 
@@ -429,8 +466,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         else
           tma_load_2d(dst, map, x, y, &bars->full[s]);
       };
+      if (GROUPED) read_lists(), waited = true;
       for (int tile = worker; tile < out_tiles && ok; tile += workers) {
-        const int m0 = item_m0(tile), n0 = item_n0(tile) + (PAIR ? static_cast<int>(rank) * BN : 0);
+        int m0 = item_m0(tile), n0 = item_n0(tile) + (PAIR ? static_cast<int>(rank) * BN : 0);
+        if (GROUPED) {
+          int m_end, g;
+          group_tile(tile, m0, m_end, g);
+          n0 += g * N;  // the group's rows of W
+        }
         const int kt0 = item_c0(tile) * kTilesPerChunk, kt1 = min(num_tiles, item_c1(tile) * kTilesPerChunk);
         int kt = kt0;
         if (!waited) {  // first item of this block
@@ -464,6 +507,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     if (lane == 0 && rank == 0) {  // in a pair the block of rank 0 issues for both
       uint32_t it = 0, gc = 0;  // k-tiles and chunks consumed so far
       bool ok = true;
+      read_lists();
       for (int tile = worker; tile < out_tiles && ok; tile += workers) {
         for (int c = item_c0(tile); c < item_c1(tile) && ok; ++c, ++gc) {
           const int buf = gc & 1;
@@ -516,6 +560,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     // a wide tile has two such blocks, one per group of four warps. With interleaved gate/up
     // weights the first piece holds gates and the second the up values of the same outputs.
     bw::pdl_wait();
+    read_lists();
     const int quarter = warp & 3;
     const int et = quarter * 32 + lane;  // 0..127: this thread's row of the tile
     const int blk = (warp - kFirstEpiWarp) >> 2;  // 0, or 0..1 in a wide tile
@@ -525,7 +570,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     uint32_t gc = 0;
     bool ok = true;
     for (int tile = worker; tile < out_tiles && ok; tile += workers) {
-      const int m0 = item_m0(tile), n0 = item_n0(tile);
+      int m0 = item_m0(tile), row_end = M;
+      const int n0 = item_n0(tile);
+      if (GROUPED) {
+        int g;
+        group_tile(tile, m0, row_end, g);
+      }
       const int row = m0 + et;
       for (int c = item_c0(tile); c < item_c1(tile) && ok; ++c, ++gc) {
         const int buf = gc & 1;
@@ -561,7 +611,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         }
       }
       if (!ok) break;
-      if (row >= M) continue;
+      if (row >= row_end) continue;
       if (SPLIT && num_chunks > 1) {
         // this item's chunk sum goes to scratch; a second kernel adds the chunk sums in order
         const int chunk = item_c0(tile);
@@ -839,7 +889,7 @@ struct Fused {
 // Once per device and kernel variant: the shared-memory limit of the kernel is raised and, for
 // the variant that runs pairs of blocks, the number of pairs the device runs at a time is
 // asked. Neither allocates. Returns 0 or an error; *pairs receives the number of pairs.
-template <bool SPLIT, int A_ROWS, int EPI, bool WIDE, bool PAIR = false>
+template <bool SPLIT, int A_ROWS, int EPI, bool WIDE, bool PAIR = false, bool GROUPED = false>
 int configure_tc(int* pairs = nullptr) {
   constexpr int smem_max = kSmemBudget + sizeof(Barriers) + 1024;
   constexpr int threads = WIDE ? 384 : 192;
@@ -847,7 +897,7 @@ int configure_tc(int* pairs = nullptr) {
   static bool configured[kMaxDevices] = {false};
   static int max_pairs[kMaxDevices] = {0};  // pairs that the device runs at the same time
   const int dev = current_device();
-  auto kernel = gemm_tc_kernel<SPLIT, A_ROWS, EPI, WIDE, PAIR>;
+  auto kernel = gemm_tc_kernel<SPLIT, A_ROWS, EPI, WIDE, PAIR, GROUPED>;
   if (!configured[dev]) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max);
     if (e != cudaSuccess) {
@@ -904,13 +954,13 @@ int launch_tc(const __nv_bfloat16* x, const __nv_bfloat16* w, void* y, int y_is_
   if (PAIR) {
     const unsigned pairs = static_cast<unsigned>(items < max_pairs ? items : max_pairs);
     bw::launch_pdl_cluster2(kernel, dim3(2 * pairs), dim3(threads), smem, stream, map_x, map_w, y, y_is_f32, residual, m,
-                            n, k, error_word, partials, bn);
+                            n, k, error_word, partials, bn, GroupItems{nullptr, nullptr, 0});
     return bw::launch_status();
   }
   const int sms = sm_count_of_device();
   const unsigned grid = static_cast<unsigned>(items < sms ? items : sms);
   bw::launch_pdl(kernel, dim3(grid), dim3(threads), smem, stream, map_x, map_w, y, y_is_f32, residual, m, n, k,
-                 error_word, partials, bn);
+                 error_word, partials, bn, GroupItems{nullptr, nullptr, 0});
   if (SPLIT) {
     const size_t outputs = static_cast<size_t>(m) * n;
     if (fused.mode == 2)
@@ -920,6 +970,30 @@ int launch_tc(const __nv_bfloat16* x, const __nv_bfloat16* w, void* y, int y_is_
       bw::launch_pdl(reduce_chunks_kernel, dim3(static_cast<unsigned>((outputs + 255) / 256)), dim3(256), 0, stream, partials, chunks, y,
                                                                                             y_is_f32, residual, m, n);
   }
+  return bw::launch_status();
+}
+
+// One product per group over lists of rows (see GROUPED above): wide tiles of 128 x 256, one
+// block per SM; the number of work items is read on the device from the lists.
+template <int EPI>
+int launch_tc_grouped(const __nv_bfloat16* x, const __nv_bfloat16* w, void* y, int y_is_f32, int rows, int n, int k,
+                      const int* group_off, const int* tile_prefix, int groups, int* error_word, cudaStream_t stream) {
+  constexpr int BNT = 2 * BN, threads = 384;
+  const RingShape ring = ring_shape(BM, BNT);
+  const int smem = ring.ring_bytes + static_cast<int>(sizeof(Barriers)) + 1024;
+  auto kernel = gemm_tc_kernel<false, BM, EPI, true, false, true>;
+  if (const int rc = configure_tc<false, BM, EPI, true, false, true>()) return rc;
+  CUtensorMap map_x, map_w;
+  if (!make_map(&map_x, x, rows, k, BM) || !make_map(&map_w, w, groups * n, k, BNT)) {
+    bw::set_error("grouped product (tcgen05): cuTensorMapEncodeTiled refused [%d x %d] / [%d x %d x %d]", rows, k, groups, n, k);
+    return -1;
+  }
+  const long long items = (static_cast<long long>((rows + BM - 1) / BM) + groups) * ((n + BNT - 1) / BNT);  // at most
+  const int sms = sm_count_of_device();
+  const unsigned grid = static_cast<unsigned>(items < sms ? items : sms);
+  bw::launch_pdl(kernel, dim3(grid), dim3(threads), smem, stream, map_x, map_w, y, y_is_f32,
+                 static_cast<const float*>(nullptr), rows, n, k, error_word, static_cast<float*>(nullptr), BNT,
+                 GroupItems{group_off, tile_prefix, groups});
   return bw::launch_status();
 }
 
@@ -990,6 +1064,28 @@ BW_API int bw_bf16_linear_tc(const __nv_bfloat16* x, const __nv_bfloat16* w, voi
   const Fused none;
   if (y_is_f32) return launch_tc_rows<2>(x, w, y, 1, residual, m, n, k, word, partials, none, stream);
   return launch_tc_rows<0>(x, w, y, 0, nullptr, m, n, k, word, partials, none, stream);
+}
+
+// Grouped products on the tcgen05 kernel: y[i] = x[i] W_g^T for the rows i of group g, x holding
+// the rows group by group (group_off[groups + 1]), w [groups][n][k], tile_prefix[groups + 1] the
+// tiles of 128 rows before each group. Usable when n is a multiple of 64, rows start on 16 bytes
+// and y on 32.
+BW_API int bw_bf16_linear_tc_grouped_usable(const void* x, const void* w, const void* y, int n, int k) {
+  return bw_bf16_linear_tc_usable(x, w, k) && n % 64 == 0 && reinterpret_cast<uintptr_t>(y) % 32 == 0;
+}
+
+BW_API int bw_bf16_linear_tc_grouped(const __nv_bfloat16* x, const __nv_bfloat16* w, void* y, int y_is_f32, int rows,
+                                     int n, int k, const int* group_off, const int* tile_prefix, int groups,
+                                     cudaStream_t stream) {
+  if (rows <= 0 || n <= 0 || groups <= 0) return 0;
+  if (!bw_bf16_linear_tc_grouped_usable(x, w, y, n, k)) {
+    bw::set_error("grouped product (tcgen05): n must be a multiple of 64, rows must start on 16 bytes, y on 32");
+    return -1;
+  }
+  int* word = bw::failure_word();
+  if (!word) return -1;
+  if (y_is_f32) return launch_tc_grouped<2>(x, w, y, 1, rows, n, k, group_off, tile_prefix, groups, word, stream);
+  return launch_tc_grouped<0>(x, w, y, 0, rows, n, k, group_off, tile_prefix, groups, word, stream);
 }
 
 // h[m][n / 2] = SwiGLU of x W^T for gate/up weights interleaved in blocks of 64 rows

@@ -298,11 +298,12 @@ latent_attention_merge_kernel(const float* __restrict__ part, const int* __restr
 // the weights enter the second product in two bfloat16 parts, p = hi + lo with lo = p - hi, so
 // that what multiplies the latents carries 16 bits of the float32 weight and not 8. The latents
 // of the tile (the first `rank` columns of the same shared-memory rows) are the second
-// product's right operand. With CS = 2 a second set of four warps repeats the scores and owns
-// the other half of the latent columns (a warp's accumulators are 16 x NT * 8 floats).
+// product's right operand. With CS = 2 a second set of four warps owns the other half of the
+// latent columns (a warp's accumulators are 16 x NT * 8 floats); each set forms the scores of
+// half of a tile's keys and both read the whole tile's scores back from shared memory.
 // With `part` the block covers one span of keys and leaves (maximum, sum, unnormalised sum of
 // latents) per query for the merge; else it writes the finished rows.
-constexpr int kTcKeys = 32, kTcQueries = 64;
+constexpr int kTcKeys = 32, kTcQueries = 64, kScoreRow = kTcKeys + 8;  // 40 floats: rows 8 apart fall on other banks
 
 template <int NT, int CS>
 __global__ void __launch_bounds__(128 * CS)
@@ -317,6 +318,7 @@ latent_attention_tc_kernel(const act_t* __restrict__ q, int q_stride, const act_
   const int dk = rank + rot_dim, rs = dk + 8;  // row stride in elements: an odd number of 16-byte pieces
   __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(raw);
   __nv_bfloat16* ks = qs + kTcQueries * rs;   // two tiles of kTcKeys rows
+  float* ss = reinterpret_cast<float*>(ks + 2 * kTcKeys * rs);  // CS == 2: a tile's scores, [queries][kScoreRow]
   const int t = blockIdx.x, sp = blockIdx.z;
   const int seq = tile_seq[t], row0 = tile_row0[t], rows = tile_rows[t];
   const int h0 = blockIdx.y * hb;
@@ -371,15 +373,43 @@ latent_attention_tc_kernel(const act_t* __restrict__ q, int q_stride, const act_
     float sc[4][4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.0f;
-    for (int kk = 0; kk < dk; kk += 16) {
-      uint32_t a[4], b0[4], b1[4];
-      bw::ldsm4(a, bw::smem_addr(qs + (wq * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * rs + kk + 8 * (lane >> 4)));
-      bw::ldsm4(b0, bw::smem_addr(kt + ((lane & 7) + 8 * (lane >> 4)) * rs + kk + 8 * ((lane >> 3) & 1)));
-      bw::ldsm4(b1, bw::smem_addr(kt + (16 + (lane & 7) + 8 * (lane >> 4)) * rs + kk + 8 * ((lane >> 3) & 1)));
-      bw::mma16816(sc[0], a, b0[0], b0[1]);
-      bw::mma16816(sc[1], a, b0[2], b0[3]);
-      bw::mma16816(sc[2], a, b1[0], b1[1]);
-      bw::mma16816(sc[3], a, b1[2], b1[3]);
+    if constexpr (CS == 1) {
+      for (int kk = 0; kk < dk; kk += 16) {
+        uint32_t a[4], b0[4], b1[4];
+        bw::ldsm4(a, bw::smem_addr(qs + (wq * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * rs + kk + 8 * (lane >> 4)));
+        bw::ldsm4(b0, bw::smem_addr(kt + ((lane & 7) + 8 * (lane >> 4)) * rs + kk + 8 * ((lane >> 3) & 1)));
+        bw::ldsm4(b1, bw::smem_addr(kt + (16 + (lane & 7) + 8 * (lane >> 4)) * rs + kk + 8 * ((lane >> 3) & 1)));
+        bw::mma16816(sc[0], a, b0[0], b0[1]);
+        bw::mma16816(sc[1], a, b0[2], b0[3]);
+        bw::mma16816(sc[2], a, b1[0], b1[1]);
+        bw::mma16816(sc[3], a, b1[2], b1[3]);
+      }
+    } else {
+      // each set of warps forms the scores of half of the tile's keys and hands them to the other
+      // through shared memory (a score is one accumulator chain either way)
+      float half[2][4];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) half[j][0] = half[j][1] = half[j][2] = half[j][3] = 0.0f;
+      for (int kk = 0; kk < dk; kk += 16) {
+        uint32_t a[4], b[4];
+        bw::ldsm4(a, bw::smem_addr(qs + (wq * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * rs + kk + 8 * (lane >> 4)));
+        bw::ldsm4(b, bw::smem_addr(kt + (16 * cs + (lane & 7) + 8 * (lane >> 4)) * rs + kk + 8 * ((lane >> 3) & 1)));
+        bw::mma16816(half[0], a, b[0], b[1]);
+        bw::mma16816(half[1], a, b[2], b[3]);
+      }
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        float* dst = ss + qa * kScoreRow + 16 * cs + 8 * j + 2 * (lane & 3);
+        *reinterpret_cast<float2*>(dst) = make_float2(half[j][0], half[j][1]);
+        *reinterpret_cast<float2*>(dst + 8 * kScoreRow) = make_float2(half[j][2], half[j][3]);
+      }
+      __syncthreads();
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float* src = ss + qa * kScoreRow + 8 * j + 2 * (lane & 3);
+        const float2 u = *reinterpret_cast<const float2*>(src), v = *reinterpret_cast<const float2*>(src + 8 * kScoreRow);
+        sc[j][0] = u.x, sc[j][1] = u.y, sc[j][2] = v.x, sc[j][3] = v.y;
+      }
     }
     float ta = -INFINITY, tb = -INFINITY;
 #pragma unroll
@@ -603,7 +633,7 @@ BW_API int BW_FN(latent_attention_force_plain)(int on) {
 // start on 16 bytes).
 BW_API int BW_FN(latent_attention_tc_tile_rows)(int heads, int rank, int rot_dim, int q_stride) {
   const int dk = rank + rot_dim;
-  const size_t smem = static_cast<size_t>(kTcQueries + 2 * kTcKeys) * (dk + 8) * 2;
+  const size_t smem = static_cast<size_t>(kTcQueries + 2 * kTcKeys) * (dk + 8) * 2 + kTcQueries * kScoreRow * 4;
   if (g_force_plain_attention || rank % 8 || dk % 16 || rank > 512 || q_stride % 8 || smem > 200 * 1024) return 0;
   return heads >= kTcQueries ? 1 : kTcQueries / heads;
 }
@@ -634,7 +664,7 @@ BW_API int BW_FN(latent_attention_tc)(const act_t* q, int q_stride, const act_t*
   }
   const int dk = rank + rot_dim;
   const int hb = heads < kTcQueries ? heads : kTcQueries;
-  const size_t smem = static_cast<size_t>(kTcQueries + 2 * kTcKeys) * (dk + 8) * 2;
+  const size_t smem = static_cast<size_t>(kTcQueries + 2 * kTcKeys) * (dk + 8) * 2 + kTcQueries * kScoreRow * 4;
   int spans = 1, span = 1 << 30;
   if (scratch) spans = BW_FN(latent_attention_tc_spans)(tiles, heads, max_keys, &span);
   dim3 grid(tiles, (heads + hb - 1) / hb, spans);

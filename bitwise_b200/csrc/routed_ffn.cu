@@ -98,8 +98,8 @@ route_kernel(const float* __restrict__ z, const float* __restrict__ correction, 
 
 // ---------------------------------------------------------------------------------------
 // One block. pairs = n * top entries of `chosen`. Outputs: group_off[E + 1] (where each
-// expert's list begins), tile_prefix[E + 1] (tiles of `tile_rows` list entries before each
-// expert), order[pairs] (the pairs expert by expert, ascending inside an expert) and
+// expert's list begins), tile_prefix[2][E + 1] (tiles of `tile_rows` list entries before each
+// expert, then tiles of twice as many), order[pairs] (the pairs expert by expert, ascending inside an expert) and
 // place[pairs] (where a pair stands in that order).
 __global__ void __launch_bounds__(1024)
 group_rows_kernel(const int* __restrict__ chosen, int pairs, int experts, int tile_rows, int* __restrict__ group_off,
@@ -111,13 +111,13 @@ group_rows_kernel(const int* __restrict__ chosen, int pairs, int experts, int ti
   for (int p = threadIdx.x; p < pairs; p += blockDim.x) atomicAdd(&cnt[chosen[p]], 1);
   __syncthreads();
   if (threadIdx.x == 0) {
-    int rows = 0, tiles = 0;
+    int rows = 0, tiles = 0, big = 0;
     for (int e = 0; e < experts; ++e) {
       const int c = cnt[e];
-      group_off[e] = rows, tile_prefix[e] = tiles, cnt[e] = rows;
-      rows += c, tiles += (c + tile_rows - 1) / tile_rows;
+      group_off[e] = rows, tile_prefix[e] = tiles, tile_prefix[experts + 1 + e] = big, cnt[e] = rows;
+      rows += c, tiles += (c + tile_rows - 1) / tile_rows, big += (c + 2 * tile_rows - 1) / (2 * tile_rows);
     }
-    group_off[experts] = rows, tile_prefix[experts] = tiles;
+    group_off[experts] = rows, tile_prefix[experts] = tiles, tile_prefix[2 * experts + 1] = big;
   }
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
@@ -235,20 +235,27 @@ grouped_linear_kernel(const act_t* __restrict__ x, int x_stride, int x_group_col
 
 #if BW_ACT_BF16
 // The same product on the tensor cores (bfloat16 in, float32 accumulators that walk k in
-// ascending steps of 16): tiles of 64 list entries x 64 outputs by four warps, k in slices of
-// 32 through a ring of three cp.async stages. For rows that start on 16 bytes (k, the row
+// ascending steps of 16): tiles of BM list entries x BN outputs by WM x WN warps, k in slices of
+// 32 through a ring of cp.async stages. 64 x 64 by four warps for short lists (decode steps), 128 x
+// 128 by eight warps where the lists are long. For rows that start on 16 bytes (k, the row
 // strides and the groups' column offsets multiples of 8).
-constexpr int kMmaStages = 3, kMmaK = 32, kMmaRow = kMmaK + 8;  // 80-byte rows: ldmatrix without bank conflicts
+constexpr int kMmaK = 32, kMmaRow = kMmaK + 8;  // 80-byte rows: ldmatrix without bank conflicts
 
-template <typename OutT>
-__global__ void __launch_bounds__(128)
+template <typename OutT, int BM, int BN, int WM, int WN, int STAGES>
+__global__ void __launch_bounds__(WM * WN * 32)
 grouped_linear_mma_kernel(const act_t* __restrict__ x, int x_stride, int x_group_cols, const int* __restrict__ order,
                           int order_div, const act_t* __restrict__ w, OutT* out, int o_stride, int o_group_cols,
                           const int* __restrict__ group_off, const int* __restrict__ tile_prefix, int uniform_rows,
                           int groups, int n, int k) {
   bw::pdl_enter();
-  __shared__ __align__(16) __nv_bfloat16 xs[kMmaStages][kTile][kMmaRow];
-  __shared__ __align__(16) __nv_bfloat16 ws[kMmaStages][kTile][kMmaRow];
+  constexpr int THREADS = WM * WN * 32;
+  constexpr int TM = BM / WM, TN = BN / WN, MI = TM / 16, NI = TN / 8;
+  constexpr int XQ = BM * 4 / THREADS, WQ = BN * 4 / THREADS;  // 16-byte pieces a thread copies per slice
+  static_assert(NI % 2 == 0 && XQ >= 1 && WQ >= 1, "tile shape");
+  extern __shared__ __align__(16) unsigned char raw[];
+  typedef __nv_bfloat16 (*Tile)[kMmaRow];
+  __nv_bfloat16* xs_base = reinterpret_cast<__nv_bfloat16*>(raw);
+  __nv_bfloat16* ws_base = xs_base + STAGES * BM * kMmaRow;
   __shared__ int s_group;
   int g, i0, i_end;
   if (group_off) {
@@ -268,93 +275,143 @@ grouped_linear_mma_kernel(const act_t* __restrict__ x, int x_stride, int x_group
     __syncthreads();
     g = s_group;
     if (g < 0) return;
-    i0 = group_off[g] + (blockIdx.x - tile_prefix[g]) * kTile;
+    i0 = group_off[g] + (blockIdx.x - tile_prefix[g]) * BM;
     i_end = group_off[g + 1];
   } else {
-    const int tiles = (uniform_rows + kTile - 1) / kTile;
+    const int tiles = (uniform_rows + BM - 1) / BM;
     g = blockIdx.x / tiles;
-    i0 = (blockIdx.x - g * tiles) * kTile;
+    i0 = (blockIdx.x - g * tiles) * BM;
     i_end = uniform_rows;
   }
-  const int j0 = blockIdx.y * kTile;
+  const int j0 = blockIdx.y * BN;
   const act_t* wg = w + static_cast<size_t>(g) * n * k;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int wm = (warp >> 1) * 32, wn = (warp & 1) * 32;
-  // a thread copies piece (tid % 4) of rows tid / 4 and tid / 4 + 32 of both tiles
+  const int wm = (warp / WN) * TM, wn = (warp % WN) * TN;
+  // a thread copies piece (tid % 4) of rows tid / 4 + (THREADS / 4) q of both tiles
   const int piece = tid & 3, lr = tid >> 2;
-  const act_t* xrow[2];
-  const act_t* wrow[2];
+  const act_t* xrow[XQ];
+  const act_t* wrow[WQ];
 #pragma unroll
-  for (int q = 0; q < 2; ++q) {
-    const int i = i0 + lr + 32 * q;
+  for (int q = 0; q < XQ; ++q) {
+    const int i = i0 + lr + (THREADS / 4) * q;
     xrow[q] = nullptr;
     if (i < i_end) {
       const int src = order ? order[i] / order_div : i;
       xrow[q] = x + static_cast<size_t>(src) * x_stride + (group_off ? 0 : g * x_group_cols);
     }
-    const int j = j0 + lr + 32 * q;
+  }
+#pragma unroll
+  for (int q = 0; q < WQ; ++q) {
+    const int j = j0 + lr + (THREADS / 4) * q;
     wrow[q] = j < n ? wg + static_cast<size_t>(j) * k : nullptr;
   }
   const int slices = (k + kMmaK - 1) / kMmaK;
   auto load = [&](int slice) {
-    const int st = slice % kMmaStages, kk = slice * kMmaK + piece * 8;
+    const int st = slice % STAGES, kk = slice * kMmaK + piece * 8;
+    Tile xs = reinterpret_cast<Tile>(xs_base + st * BM * kMmaRow);
+    Tile ws = reinterpret_cast<Tile>(ws_base + st * BN * kMmaRow);
 #pragma unroll
-    for (int q = 0; q < 2; ++q) {
-      const bool vx = xrow[q] && kk < k, vw = wrow[q] && kk < k;
-      bw::copy16_async(bw::smem_addr(&xs[st][lr + 32 * q][piece * 8]), vx ? xrow[q] + kk : x, vx);
-      bw::copy16_async(bw::smem_addr(&ws[st][lr + 32 * q][piece * 8]), vw ? wrow[q] + kk : w, vw);
+    for (int q = 0; q < XQ; ++q) {
+      const bool v = xrow[q] && kk < k;
+      bw::copy16_async(bw::smem_addr(&xs[lr + (THREADS / 4) * q][piece * 8]), v ? xrow[q] + kk : x, v);
+    }
+#pragma unroll
+    for (int q = 0; q < WQ; ++q) {
+      const bool v = wrow[q] && kk < k;
+      bw::copy16_async(bw::smem_addr(&ws[lr + (THREADS / 4) * q][piece * 8]), v ? wrow[q] + kk : w, v);
     }
   };
-  float acc[2][4][4];
+  float acc[MI][NI][4];
 #pragma unroll
-  for (int a = 0; a < 2; ++a)
+  for (int a = 0; a < MI; ++a)
 #pragma unroll
-    for (int b = 0; b < 4; ++b)
+    for (int b = 0; b < NI; ++b)
 #pragma unroll
       for (int c = 0; c < 4; ++c) acc[a][b][c] = 0.0f;
 #pragma unroll
-  for (int s = 0; s < kMmaStages - 1; ++s) {
+  for (int s = 0; s < STAGES - 1; ++s) {
     if (s < slices) load(s);
     bw::copies_commit();
   }
   for (int slice = 0; slice < slices; ++slice) {
-    bw::copies_wait<kMmaStages - 2>();
+    bw::copies_wait<STAGES - 2>();
     __syncthreads();
-    if (slice + kMmaStages - 1 < slices) load(slice + kMmaStages - 1);
+    if (slice + STAGES - 1 < slices) load(slice + STAGES - 1);
     bw::copies_commit();
-    const int st = slice % kMmaStages;
+    const int st = slice % STAGES;
+    Tile xs = reinterpret_cast<Tile>(xs_base + st * BM * kMmaRow);
+    Tile ws = reinterpret_cast<Tile>(ws_base + st * BN * kMmaRow);
 #pragma unroll
     for (int ks = 0; ks < kMmaK / 16; ++ks) {
-      uint32_t a[2][4], b[2][4];
+      uint32_t a[MI][4], b[NI / 2][4];
 #pragma unroll
-      for (int mi = 0; mi < 2; ++mi)
-        bw::ldsm4(a[mi], bw::smem_addr(&xs[st][wm + mi * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)][ks * 16 + 8 * (lane >> 4)]));
+      for (int mi = 0; mi < MI; ++mi)
+        bw::ldsm4(a[mi], bw::smem_addr(&xs[wm + mi * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)][ks * 16 + 8 * (lane >> 4)]));
 #pragma unroll
-      for (int np = 0; np < 2; ++np)
-        bw::ldsm4(b[np], bw::smem_addr(&ws[st][wn + np * 16 + (lane & 7) + 8 * (lane >> 4)][ks * 16 + 8 * ((lane >> 3) & 1)]));
+      for (int np = 0; np < NI / 2; ++np)
+        bw::ldsm4(b[np], bw::smem_addr(&ws[wn + np * 16 + (lane & 7) + 8 * (lane >> 4)][ks * 16 + 8 * ((lane >> 3) & 1)]));
 #pragma unroll
-      for (int mi = 0; mi < 2; ++mi)
+      for (int mi = 0; mi < MI; ++mi)
 #pragma unroll
-        for (int ni = 0; ni < 4; ++ni) bw::mma16816(acc[mi][ni], a[mi], b[ni >> 1][(ni & 1) * 2], b[ni >> 1][(ni & 1) * 2 + 1]);
+        for (int ni = 0; ni < NI; ++ni) bw::mma16816(acc[mi][ni], a[mi], b[ni >> 1][(ni & 1) * 2], b[ni >> 1][(ni & 1) * 2 + 1]);
     }
   }
   bw::copies_wait<0>();
 #pragma unroll
-  for (int mi = 0; mi < 2; ++mi)
+  for (int mi = 0; mi < MI; ++mi)
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
       const int i = i0 + wm + mi * 16 + (lane >> 2) + 8 * half;
       if (i >= i_end) continue;
       OutT* orow = out + static_cast<size_t>(i) * o_stride + (group_off ? 0 : g * o_group_cols);
 #pragma unroll
-      for (int ni = 0; ni < 4; ++ni) {
+      for (int ni = 0; ni < NI; ++ni) {
         const int j = j0 + wn + ni * 8 + 2 * (lane & 3);
         if (j < n) orow[j] = bw::from_f<OutT>(acc[mi][ni][2 * half]);
         if (j + 1 < n) orow[j + 1] = bw::from_f<OutT>(acc[mi][ni][2 * half + 1]);
       }
     }
 }
+
+constexpr int kBigTile = 128;
+
+template <typename OutT, int BM, int BN, int WM, int WN, int STAGES>
+int launch_grouped_mma(dim3 grid, cudaStream_t stream, const act_t* x, int x_stride, int x_group_cols, const int* order,
+                       int order_div, const act_t* w, OutT* out, int o_stride, int o_group_cols, const int* group_off,
+                       const int* tile_prefix, int rows, int groups, int n, int k) {
+  auto kernel = grouped_linear_mma_kernel<OutT, BM, BN, WM, WN, STAGES>;
+  constexpr size_t smem = static_cast<size_t>(STAGES) * (BM + BN) * kMmaRow * sizeof(__nv_bfloat16);
+  static bool raised = false;
+  if (smem > 48 * 1024 && !raised) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) {
+      bw::set_error("grouped_linear: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
+      return static_cast<int>(e);
+    }
+    raised = true;
+  }
+  bw::launch_pdl(kernel, grid, dim3(WM * WN * 32), smem, stream, x, x_stride, x_group_cols, order, order_div, w, out,
+                 o_stride, o_group_cols, group_off, tile_prefix, rows, groups, n, k);
+  return bw::launch_status();
+}
 #endif
+
+// out[i] = x[order[i] / order_div]: the rows of a list made contiguous (16 bytes per thread where
+// the rows allow it), for products that fetch their operands as tiles of consecutive rows.
+__global__ void gather_rows_kernel(const act_t* __restrict__ x, const int* __restrict__ order, int order_div,
+                                   act_t* __restrict__ out, int k, int vec) {
+  bw::pdl_enter();
+  const int i = blockIdx.x;
+  const act_t* src = x + static_cast<size_t>(order[i] / order_div) * k;
+  act_t* dst = out + static_cast<size_t>(i) * k;
+  if (vec) {
+    constexpr int per = 16 / sizeof(act_t);
+    for (int c = threadIdx.x; c < k / per; c += blockDim.x)
+      reinterpret_cast<uint4*>(dst)[c] = reinterpret_cast<const uint4*>(src)[c];
+  } else {
+    for (int c = threadIdx.x; c < k; c += blockDim.x) dst[c] = src[c];
+  }
+}
 
 // ---------------------------------------------------------------------------------------
 __global__ void glu_clamped_kernel(const act_t* __restrict__ gate_up, act_t* __restrict__ out, int inter, float limit,
@@ -455,13 +512,28 @@ BW_API int BW_FN(grouped_linear)(const act_t* x, int x_stride, int x_group_cols,
   const bool aligned = k % 8 == 0 && x_stride % 8 == 0 && x_group_cols % 8 == 0 &&
                        reinterpret_cast<uintptr_t>(x) % 16 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0;
   if (aligned && !g_force_plain) {
+    // long lists (on average a big tile's worth of rows per group) take tiles of 128 x 128
+    const bool big = static_cast<long long>(rows) >= (group_off ? static_cast<long long>(kBigTile) * groups : kBigTile) && n >= kBigTile;
+    if (big) {
+      const long long bt = group_off ? (rows + kBigTile - 1) / kBigTile + groups
+                                     : static_cast<long long>(groups) * ((rows + kBigTile - 1) / kBigTile);
+      dim3 bgrid(static_cast<unsigned>(bt), (n + kBigTile - 1) / kBigTile);
+      const int* prefix = tile_prefix ? tile_prefix + groups + 1 : nullptr;
+      if (out_is_f32)
+        return launch_grouped_mma<float, 128, 128, 2, 4, 4>(bgrid, stream, x, x_stride, x_group_cols, order, order_div, w,
+                                                            static_cast<float*>(out), o_stride, o_group_cols, group_off,
+                                                            prefix, rows, groups, n, k);
+      return launch_grouped_mma<act_t, 128, 128, 2, 4, 4>(bgrid, stream, x, x_stride, x_group_cols, order, order_div, w,
+                                                          static_cast<act_t*>(out), o_stride, o_group_cols, group_off,
+                                                          prefix, rows, groups, n, k);
+    }
     if (out_is_f32)
-      bw::launch_pdl(grouped_linear_mma_kernel<float>, grid, dim3(128), 0, stream, x, x_stride, x_group_cols, order,
-                     order_div, w, static_cast<float*>(out), o_stride, o_group_cols, group_off, tile_prefix, rows, groups, n, k);
-    else
-      bw::launch_pdl(grouped_linear_mma_kernel<act_t>, grid, dim3(128), 0, stream, x, x_stride, x_group_cols, order,
-                     order_div, w, static_cast<act_t*>(out), o_stride, o_group_cols, group_off, tile_prefix, rows, groups, n, k);
-    return bw::launch_status();
+      return launch_grouped_mma<float, 64, 64, 2, 2, 3>(grid, stream, x, x_stride, x_group_cols, order, order_div, w,
+                                                        static_cast<float*>(out), o_stride, o_group_cols, group_off,
+                                                        tile_prefix, rows, groups, n, k);
+    return launch_grouped_mma<act_t, 64, 64, 2, 2, 3>(grid, stream, x, x_stride, x_group_cols, order, order_div, w,
+                                                      static_cast<act_t*>(out), o_stride, o_group_cols, group_off,
+                                                      tile_prefix, rows, groups, n, k);
   }
 #endif
   if (out_is_f32)
@@ -470,6 +542,15 @@ BW_API int BW_FN(grouped_linear)(const act_t* x, int x_stride, int x_group_cols,
   else
     bw::launch_pdl(grouped_linear_kernel<act_t>, grid, dim3(256), 0, stream, x, x_stride, x_group_cols, order, order_div,
                    w, static_cast<act_t*>(out), o_stride, o_group_cols, group_off, tile_prefix, rows, groups, n, k);
+  return bw::launch_status();
+}
+
+BW_API int BW_FN(gather_rows)(const act_t* x, const int* order, int order_div, act_t* out, int rows, int k,
+                              cudaStream_t stream) {
+  if (rows <= 0 || k <= 0) return 0;
+  const int per = 16 / static_cast<int>(sizeof(act_t));
+  const int vec = k % per == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0;
+  bw::launch_pdl(gather_rows_kernel, dim3(rows), dim3(128), 0, stream, x, order, order_div, out, k, vec);
   return bw::launch_status();
 }
 

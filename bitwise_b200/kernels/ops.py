@@ -708,6 +708,7 @@ class KernelOps:
     def plain_parts(self, on: bool) -> None:
         """Tests: keep latent attention and the grouped products on the plain kernels (one chain of
         fused multiply-adds per output) also where the tensor-core kernels would take the shape."""
+        self._plain_parts = bool(on)
         if self.kind == "bf16":
             lib = self._parts_lib()
             lib.bw_bf16_latent_attention_force_plain(_c_int(int(on)))
@@ -789,25 +790,45 @@ class KernelOps:
     def group_rows(self, chosen: torch.Tensor, experts: int, group_off: torch.Tensor, tile_prefix: torch.Tensor,
                    order: torch.Tensor, place: torch.Tensor) -> None:
         """The (row, choice) pairs of ``chosen`` listed expert by expert: group_off [experts + 1],
-        tile_prefix [experts + 1] (tiles of the grouped product before each expert), order [pairs]
+        tile_prefix [2, experts + 1] (tiles of the grouped product before each expert, for its
+        two tile heights), order [pairs]
         (pair index = row * top + choice), place [pairs] (where a pair stands in ``order``)."""
         pairs = chosen.numel()
         for t_, what in ((chosen, "chosen"), (group_off, "group_off"), (tile_prefix, "tile_prefix"), (order, "order"),
                          (place, "place")):
             _need(t_, torch.int32, "group_rows " + what)
-        if group_off.numel() < experts + 1 or tile_prefix.numel() < experts + 1 or order.numel() < pairs or \
+        if group_off.numel() < experts + 1 or tile_prefix.numel() < 2 * (experts + 1) or order.numel() < pairs or \
                 place.numel() < pairs:
             raise KernelError("group_rows: an output is too small")
         self._pcall("group_rows", _p(chosen), _c_int(pairs), _c_int(experts), _p(group_off), _p(tile_prefix), _p(order),
                     _p(place), self._stream())
 
+    def gather_rows(self, x: torch.Tensor, order: torch.Tensor, order_div: int, out: torch.Tensor, rows: int) -> None:
+        """out[i] = x[order[i] // order_div] for i < rows."""
+        _need(x, self.act_dtype, "gather_rows x", 2)
+        _need(out, self.act_dtype, "gather_rows out", 2)
+        _need(order, torch.int32, "gather_rows order")
+        if out.shape[1] != x.shape[1] or out.shape[0] < rows or order.numel() < rows:
+            raise KernelError("gather_rows: shapes differ")
+        self._pcall("gather_rows", _p(x), _p(order), _c_int(order_div), _p(out), _c_int(rows), _c_int(x.shape[1]),
+                    self._stream())
+
+    def grouped_takes_tiles(self, rows: int, groups: int, n: int, k: int) -> bool:
+        """Whether a grouped product over lists of this size runs on the tcgen05 kernel, which
+        fetches tiles of consecutive rows (the caller then offers ``sorted_x`` to ``grouped_linear``):
+        the serving precision, lists of on average a tile of 128 rows or more, n a multiple of 64."""
+        return (self.kind == "bf16" and not getattr(self, "_plain_parts", False) and rows >= 128 * groups
+                and n % 64 == 0 and k % 8 == 0)
+
     def grouped_linear(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, rows: int, x_group_cols: int = 0,
-                       o_group_cols: int = 0, lists=None, order_div: int = 1, gather: bool = True) -> None:
+                       o_group_cols: int = 0, lists=None, order_div: int = 1, gather: bool = True,
+                       sorted_x: Optional[torch.Tensor] = None) -> None:
         """One product per group with w [groups, n, k].  Without ``lists`` every group g takes rows
         0 .. rows-1: out[r, g * o_group_cols + j] = sum_i x[r, g * x_group_cols + i] w[g, j, i].  With
         ``lists`` = (group_off, tile_prefix, order) from ``group_rows`` entry i of group g reads row
         order[i] // order_div of x (row i when ``gather`` is False) and writes row i of out; ``rows``
-        is then the length of the list."""
+        is then the length of the list.  ``sorted_x``: scratch [rows, k] for the gathered rows, used
+        where ``grouped_takes_tiles`` says so."""
         groups, n, k = w.shape
         _need(x, self.act_dtype, "grouped_linear x", 2)
         _need(w, self.act_dtype, "grouped_linear w", 3)
@@ -825,6 +846,18 @@ class KernelOps:
                 raise KernelError("grouped_linear: widths differ from the weights'")
             if not gather:
                 order = None
+            if self.grouped_takes_tiles(rows, groups, n, k) and (order is None or sorted_x is not None):
+                # long lists: the tcgen05 product over rows made contiguous group by group
+                src = x
+                if order is not None:
+                    self.gather_rows(x, order, order_div, sorted_x, rows)
+                    src = sorted_x
+                if self.lib.bw_bf16_linear_tc_grouped_usable(_p(src), _p(w), _p(out), _c_int(n), _c_int(k)):
+                    self._call("bw_bf16_linear_tc_grouped", _p(src), _p(w), _p(out), _c_int(int(out.dtype == torch.float32)),
+                               _c_int(rows), _c_int(n), _c_int(k), _p(group_off), _p(tile_prefix[1]), _c_int(groups),
+                               self._stream())
+                    return
+                x, order, order_div = src, None, 1
         self._pcall("grouped_linear", _p(x), _c_int(x.shape[1]), _c_int(x_group_cols), _p(order), _c_int(order_div),
                     _p(w), _p(out), _c_int(int(out.dtype == torch.float32)), _c_int(out.shape[1]), _c_int(o_group_cols),
                     _p(group_off), _p(tile_prefix), _c_int(rows), _c_int(groups), _c_int(n), _c_int(k), self._stream())

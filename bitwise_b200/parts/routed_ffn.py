@@ -112,14 +112,17 @@ class RoutedFFN(FeedForward):
         chosen = ws.rows("route_chosen", n, top, torch.int32)
         weights = ws.rows("route_weights", n, top, torch.float32)
         ops.route(z, self.correction, self.groups, self.keep_groups, top, self.weight_scale, chosen, weights)
-        lists = ws.rows("route_lists", 2, self.experts + 1, torch.int32)
+        lists = ws.rows("route_lists", 3, self.experts + 1, torch.int32)
         order = ws.rows("route_order", n, top, torch.int32)
         place = ws.rows("route_place", n, top, torch.int32)
-        ops.group_rows(chosen, self.experts, lists[0], lists[1], order, place)
-        grouped = (lists[0], lists[1], order)
+        ops.group_rows(chosen, self.experts, lists[0], lists[1:3], order, place)
+        grouped = (lists[0], lists[1:3], order)
         # the chosen experts, all in one product each for gate/up and down
         gate_up = ws.rows("routed_gate_up", n, top * 2 * self.inner, act).view(pairs, 2 * self.inner)
-        ops.grouped_linear(xn, self.w_gate_up, gate_up, pairs, lists=grouped, order_div=top)
+        sorted_x = None
+        if getattr(ops, "grouped_takes_tiles", None) and ops.grouped_takes_tiles(pairs, self.experts, 2 * self.inner, self.width):
+            sorted_x = ws.rows("routed_x", n, top * self.width, act).view(pairs, self.width)
+        ops.grouped_linear(xn, self.w_gate_up, gate_up, pairs, lists=grouped, order_div=top, sorted_x=sorted_x)
         h = ws.rows("routed_h", n, top * self.inner, act).view(pairs, self.inner)
         ops.glu_clamped(gate_up, h, self.limit, self.alpha)
         y = ws.rows("routed_y", n, top * self.width, torch.float32).view(pairs, self.width)

@@ -254,7 +254,8 @@ def test_route(experts, groups, keep, top):
 
 
 @pytest.mark.parametrize("dtype,width,inner,plain", [("float32", 50, 19, False), ("bfloat16", 50, 19, False),
-                                                     ("bfloat16", 72, 40, False), ("bfloat16", 72, 40, True)])
+                                                     ("bfloat16", 72, 40, False), ("bfloat16", 72, 40, True), ("bfloat16", 136, 200, False),
+                                                     ("bfloat16", 192, 96, False)])
 def test_grouped_products_activation_and_combination(dtype, width, inner, plain):
     # widths that are multiples of 8 take the tensor-core kernel on the serving precision
     ops = ops_of(dtype)
@@ -267,13 +268,15 @@ def test_grouped_products_activation_and_combination(dtype, width, inner, plain)
 
 def _grouped_case(ops, dtype, width, inner):
     g = torch.Generator().manual_seed(5)
-    n, top, experts = 150, 3, 7                              # expert 4 is never chosen, others get unequal shares
+    n, top, experts = (150, 3, 7) if width < 100 else (700, 3, 7)   # expert 4 is never chosen, others get unequal shares
+    # (with 700 rows the lists are long enough for the tiles of 128 x 128, and where the widths are
+    # multiples of 64 for the tcgen05 product over gathered rows)
     chosen = torch.stack([torch.tensor([0, 1, 2, 3, 5, 6])[torch.randperm(6, generator=g)[:top]] for _ in range(n)])
     chosen[:100, 0] = 5                                     # more than one tile of rows for one expert
     chosen[:100, 1:] = torch.tensor([0, 1])
     chosen = chosen.to(torch.int32).to(DEV)
     off = torch.empty(experts + 1, dtype=torch.int32, device=DEV)
-    tiles = torch.empty(experts + 1, dtype=torch.int32, device=DEV)
+    tiles = torch.empty(2, experts + 1, dtype=torch.int32, device=DEV)
     order = torch.empty(n * top, dtype=torch.int32, device=DEV)
     place = torch.empty(n * top, dtype=torch.int32, device=DEV)
     ops.group_rows(chosen, experts, off, tiles, order, place)
@@ -288,7 +291,10 @@ def _grouped_case(ops, dtype, width, inner):
     w1 = (torch.randn(experts, 2 * inner, width, generator=g) / math.sqrt(width) * 2).to(act(dtype))
     w2 = (torch.randn(experts, width, inner, generator=g) / math.sqrt(inner)).to(act(dtype))
     gate_up = torch.empty(n * top, 2 * inner, dtype=act(dtype), device=DEV)
-    ops.grouped_linear(x.to(DEV), w1.to(DEV), gate_up, n * top, lists=(off, tiles, order), order_div=top)
+    sorted_x = torch.empty(n * top, width, dtype=act(dtype), device=DEV)
+    ops.grouped_linear(x.to(DEV), w1.to(DEV), gate_up, n * top, lists=(off, tiles, order), order_div=top, sorted_x=sorted_x)
+    if ops.grouped_takes_tiles(n * top, experts, 2 * inner, width):
+        assert torch.equal(sorted_x.cpu(), x[(order.cpu() // top).long()])
     src = (o // top).long()
     want_gu = torch.einsum("ik,ijk->ij", x.to(F64)[src], w1.to(F64)[flat[o.long()].long()])
     close(gate_up, want_gu, dtype, "gate and up of the chosen experts")
