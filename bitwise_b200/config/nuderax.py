@@ -68,8 +68,6 @@ class LatentMixerConfig:
             raise ConfigError(f"config.json: {where}.rot.base must be positive")
         if kind == "latent_attention_2" and c.q_rank is None:
             raise ConfigError(f"config.json: {where} is of type latent_attention_2 and lacks q_rank")
-        if kind == "latent_attention_2" and c.kv_from is not None:
-            raise ConfigError(f"config.json: {where}: kv_from belongs to the type latent_attention")
         return c
 
     def to_json(self) -> dict:

@@ -9,8 +9,9 @@
 // Kernels: the store (root-mean-square norm of the latent, rotation of the shared key part,
 // write into the page), the rotation of the queries' rotated parts, attention for query tiles
 // (prompt portions and steps of few rows alike), and attention split over the keys for steps of
-// single rows, with its merge. Scores, softmax weights, sums and rotations are float32 in both
-// precisions.
+// single rows, with its merge; each attention once on the CUDA cores (both precisions) and once
+// on the tensor cores (bfloat16). Scores, softmax weights, sums and rotations are float32 in
+// both precisions.
 #include "bw_act.cuh"
 #include "bw_mma.cuh"
 
@@ -96,10 +97,6 @@ rotate_heads_kernel(const act_t* __restrict__ q, int q_stride, int head_stride, 
 constexpr int kWarps = 8;
 constexpr int kKeys = 32;
 constexpr int kThreads = kWarps * 32;
-
-struct QueryState {
-  float m, l;
-};
 
 // One tile of keys in shared memory (`keys`, rows of `ks` floats) against the query `qv`
 // (`dk` floats in shared memory) of position `pq`: updates m, l and acc (entry i of acc is

@@ -10,8 +10,10 @@
 //  * grouped_linear: out[i] = x[source(i)] W_g^T for the list entries i of every group g, W
 //    stored [groups, n, k]. With a list the groups are the experts (rows of unequal number);
 //    without, every group takes every row and reads and writes its own columns (one product per
-//    head). An output is one chain of fused multiply-adds over k in ascending order, whatever
-//    tile it sits in.
+//    head). An output is one chain over k in ascending order, whatever tile it sits in: fused
+//    multiply-adds on the CUDA cores, or on the serving precision tensor-core steps of 16.
+//  * gather_rows: the rows of a list made contiguous, for the tcgen05 product over long lists
+//    (bf16_gemm_tc.cu), which fetches tiles of consecutive rows.
 //  * glu_clamped: y = g' sigmoid(alpha g') (u' + 1), g' = min(g, limit), u' = clamp(u, +-limit).
 //  * combine: x += d + sum_j weight_j * y[place of (row, j)], the sum in the order of choice.
 #include "bw_act.cuh"
@@ -22,8 +24,8 @@
 namespace {
 
 // ---------------------------------------------------------------------------------------
-// One warp per row. Shared memory per warp: scores s[E], choice scores c[E] (taken experts are
-// set to -inf as the choice goes on), group scores [groups].
+// One warp per row. Shared memory per warp: scores s[E] (a taken expert's is set to -1), choice
+// scores c[E] (-inf for the experts of groups that do not stay), group scores [groups].
 __global__ void __launch_bounds__(128)
 route_kernel(const float* __restrict__ z, const float* __restrict__ correction, int n, int experts, int groups,
              int keep, int top, float weight_scale, int* __restrict__ chosen, float* __restrict__ weights) {
