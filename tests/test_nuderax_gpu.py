@@ -483,3 +483,14 @@ def test_greedy_generation_through_the_engine(dtype):
                 assert row.max() - row[t] <= 0.05 * np.abs(row).max(), "the chosen token is no near-maximum"
             seq.append(t)
     assert eng.manager.all_free()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_simulated_traces_reproduce_requests_run_alone(dtype):
+    # the engine's simulator: random requests, budgets and pools; a request's tokens and the
+    # fingerprint of its logits must be those it yields alone on an idle engine (contexts stay
+    # below the 256 keys from which single rows change kernels, so cuts agree bit for bit here)
+    from bitwise_b200.engine.simulate import run_traces
+    out = run_traces(model_of("a", dtype), traces=8, seed=5)
+    assert out.traces == 8 and out.requests_checked > 10
+    assert out.violations == 0, (out.token_mismatch, out.fingerprint_mismatch, out.hangs, out.leaks)
