@@ -99,7 +99,8 @@ route_kernel(const float* __restrict__ z, const float* __restrict__ correction, 
 }
 
 // ---------------------------------------------------------------------------------------
-// One block. pairs = n * top entries of `chosen`. Outputs: group_off[E + 1] (where each
+// pairs = n * top entries of `chosen`. Every block counts the experts' pairs for itself (shared-memory
+// atomics; the counts do not depend on their order); the placing is shared between the blocks. Outputs: group_off[E + 1] (where each
 // expert's list begins), tile_prefix[2][E + 1] (tiles of `tile_rows` list entries before each
 // expert, then tiles of twice as many), order[pairs] (the pairs expert by expert, ascending inside an expert) and
 // place[pairs] (where a pair stands in that order).
@@ -113,16 +114,20 @@ group_rows_kernel(const int* __restrict__ chosen, int pairs, int experts, int ti
   for (int p = threadIdx.x; p < pairs; p += blockDim.x) atomicAdd(&cnt[chosen[p]], 1);
   __syncthreads();
   if (threadIdx.x == 0) {
+    const bool writes = blockIdx.x == 0;  // every block counts, the first one writes the lists
     int rows = 0, tiles = 0, big = 0;
     for (int e = 0; e < experts; ++e) {
       const int c = cnt[e];
-      group_off[e] = rows, tile_prefix[e] = tiles, tile_prefix[experts + 1 + e] = big, cnt[e] = rows;
+      if (writes) group_off[e] = rows, tile_prefix[e] = tiles, tile_prefix[experts + 1 + e] = big;
+      cnt[e] = rows;
       rows += c, tiles += (c + tile_rows - 1) / tile_rows, big += (c + 2 * tile_rows - 1) / (2 * tile_rows);
     }
-    group_off[experts] = rows, tile_prefix[experts] = tiles, tile_prefix[2 * experts + 1] = big;
+    if (writes) group_off[experts] = rows, tile_prefix[experts] = tiles, tile_prefix[2 * experts + 1] = big;
   }
   __syncthreads();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  // a warp places the pairs of one expert; the experts are dealt to the warps of all blocks
+  const int lane = threadIdx.x & 31, warps = (blockDim.x >> 5) * gridDim.x;
+  const int warp = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   for (int e = warp; e < experts; e += warps) {
     int at = cnt[e];
     for (int p0 = 0; p0 < pairs; p0 += 32) {
@@ -485,8 +490,11 @@ BW_API int BW_FN(group_rows)(const int* chosen, int pairs, int experts, int* gro
     bw::set_error("group_rows: %d experts", experts);
     return -1;
   }
-  bw::launch_pdl(group_rows_kernel, dim3(1), dim3(1024), static_cast<size_t>(experts + 1) * sizeof(int), stream, chosen,
-                 pairs, experts, kTile, group_off, tile_prefix, order, place);
+  // one block for short lists; for long ones a block per 8 experts (a warp walks all pairs once per expert)
+  const int blocks = pairs < 2048 ? 1 : (experts + 7) / 8;
+  const int threads = blocks == 1 ? 1024 : 256;
+  bw::launch_pdl(group_rows_kernel, dim3(blocks), dim3(threads), static_cast<size_t>(experts + 1) * sizeof(int), stream,
+                 chosen, pairs, experts, kTile, group_off, tile_prefix, order, place);
   return bw::launch_status();
 }
 
