@@ -62,17 +62,20 @@ latent_store_kernel(const float* __restrict__ d, int d_stride, const float* __re
 }
 
 // The rotated part of every head's query: `rot_dim` entries at q[row][h * head_stride + offset],
-// turned and written to out[row][h * out_head_stride + out_offset]. Grid: (row, head).
-__global__ void __launch_bounds__(64)
+// turned and written to out[row][h * out_head_stride + out_offset]. One block per row; a thread
+// takes a pair of one head.
+__global__ void __launch_bounds__(128)
 rotate_heads_kernel(const act_t* __restrict__ q, int q_stride, int head_stride, int offset, act_t* out, int o_stride,
-                    int out_head_stride, int out_offset, int rot_dim, int pairs, const int* __restrict__ pos,
+                    int out_head_stride, int out_offset, int heads, int rot_dim, int pairs, const int* __restrict__ pos,
                     const float* __restrict__ cos_t, const float* __restrict__ sin_t) {
   bw::pdl_enter();
-  const int r = blockIdx.x, h = blockIdx.y;
+  const int r = blockIdx.x;
   const int p = pos[r];
-  const act_t* src = q + static_cast<size_t>(r) * q_stride + h * head_stride + offset;
-  act_t* dst = out + static_cast<size_t>(r) * o_stride + h * out_head_stride + out_offset;
-  for (int i = threadIdx.x; i < (rot_dim + 1) / 2; i += blockDim.x) {
+  const int half = (rot_dim + 1) / 2;
+  for (int item = threadIdx.x; item < heads * half; item += blockDim.x) {
+    const int h = item / half, i = item - h * half;
+    const act_t* src = q + static_cast<size_t>(r) * q_stride + h * head_stride + offset;
+    act_t* dst = out + static_cast<size_t>(r) * o_stride + h * out_head_stride + out_offset;
     const float u = bw::to_f(src[2 * i]);
     if (2 * i + 1 >= rot_dim) {
       dst[2 * i] = bw::from_f<act_t>(u);
@@ -531,12 +534,12 @@ BW_API int BW_FN(rotate_heads)(const act_t* q, int q_stride, int head_stride, in
                                int out_head_stride, int out_offset, int n, int heads, int rot_dim, int pairs,
                                const int* pos, const float* cos_t, const float* sin_t, cudaStream_t stream) {
   if (n <= 0 || heads <= 0 || rot_dim <= 0) return 0;
-  if (2 * pairs > rot_dim || (pairs > 0 && !cos_t) || heads > 65535) {
+  if (2 * pairs > rot_dim || (pairs > 0 && !cos_t)) {
     bw::set_error("rotate_heads: %d heads, rotated part %d, %d pairs", heads, rot_dim, pairs);
     return -1;
   }
-  bw::launch_pdl(rotate_heads_kernel, dim3(n, heads), dim3(64), 0, stream, q, q_stride, head_stride, offset, out,
-                 o_stride, out_head_stride, out_offset, rot_dim, pairs, pos, cos_t, sin_t);
+  bw::launch_pdl(rotate_heads_kernel, dim3(n), dim3(128), 0, stream, q, q_stride, head_stride, offset, out, o_stride,
+                 out_head_stride, out_offset, heads, rot_dim, pairs, pos, cos_t, sin_t);
   return bw::launch_status();
 }
 

@@ -130,15 +130,24 @@ group_rows_kernel(const int* __restrict__ chosen, int pairs, int experts, int ti
   const int warp = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   for (int e = warp; e < experts; e += warps) {
     int at = cnt[e];
-    for (int p0 = 0; p0 < pairs; p0 += 32) {
-      const int p = p0 + lane;
-      const bool mine = p < pairs && chosen[p] == e;
-      const unsigned mask = __ballot_sync(0xffffffffu, mine);
-      if (mine) {
-        const int i = at + __popc(mask & ((1u << lane) - 1u));
-        order[i] = p, place[p] = i;
+    for (int p0 = 0; p0 < pairs; p0 += 256) {  // eight loads in flight: the walk is a chain of memory round trips
+      int who[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int p = p0 + 32 * j + lane;
+        who[j] = p < pairs ? chosen[p] : -1;
       }
-      at += __popc(mask);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int p = p0 + 32 * j + lane;
+        const bool mine = who[j] == e;
+        const unsigned mask = __ballot_sync(0xffffffffu, mine);
+        if (mine) {
+          const int i = at + __popc(mask & ((1u << lane) - 1u));
+          order[i] = p, place[p] = i;
+        }
+        at += __popc(mask);
+      }
     }
   }
 }
@@ -421,34 +430,68 @@ __global__ void gather_rows_kernel(const act_t* __restrict__ x, const int* __res
 }
 
 // ---------------------------------------------------------------------------------------
+__device__ __forceinline__ float glu_one(float g, float u, float limit, float alpha) {
+  g = fminf(g, limit);
+  u = fminf(fmaxf(u, -limit), limit);
+  const float sig = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-__fmul_rn(alpha, g))));
+  return __fmul_rn(__fmul_rn(g, sig), __fadd_rn(u, 1.0f));
+}
+
+// Grid (row, block of columns). VEC: a thread takes 16 bytes of gate and of up (the inner size a
+// multiple of 16 bytes' worth and the buffers aligned), else one column.
+template <bool VEC>
 __global__ void glu_clamped_kernel(const act_t* __restrict__ gate_up, act_t* __restrict__ out, int inter, float limit,
                                    float alpha) {
   bw::pdl_enter();
+  constexpr int per = VEC ? 16 / static_cast<int>(sizeof(act_t)) : 1;
   const int r = blockIdx.x;
-  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * per;
   if (c >= inter) return;
   const act_t* row = gate_up + static_cast<size_t>(r) * 2 * inter;
-  const float g = fminf(bw::to_f(row[c]), limit);
-  const float u = fminf(fmaxf(bw::to_f(row[inter + c]), -limit), limit);
-  const float sig = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-__fmul_rn(alpha, g))));
-  out[static_cast<size_t>(r) * inter + c] = bw::from_f<act_t>(__fmul_rn(__fmul_rn(g, sig), __fadd_rn(u, 1.0f)));
+  act_t* dst = out + static_cast<size_t>(r) * inter + c;
+  if (VEC) {
+    const uint4 gv = *reinterpret_cast<const uint4*>(row + c), uv = *reinterpret_cast<const uint4*>(row + inter + c);
+    const act_t* g = reinterpret_cast<const act_t*>(&gv);
+    const act_t* u = reinterpret_cast<const act_t*>(&uv);
+    __align__(16) act_t o[per];
+#pragma unroll
+    for (int e = 0; e < per; ++e) o[e] = bw::from_f<act_t>(glu_one(bw::to_f(g[e]), bw::to_f(u[e]), limit, alpha));
+    *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(o);
+  } else {
+    dst[0] = bw::from_f<act_t>(glu_one(bw::to_f(row[c]), bw::to_f(row[inter + c]), limit, alpha));
+  }
 }
 
-// x[r] += d[r] + sum_j weights[r][j] * y[place[r * top + j]]; d may be null.
+// x[r] += d[r] + sum_j weights[r][j] * y[place[r * top + j]]; d may be null. VEC: four columns per
+// thread (the width a multiple of 4).
+template <bool VEC>
 __global__ void combine_kernel(float* x, const float* __restrict__ d, const float* __restrict__ y,
                                const int* __restrict__ place, const float* __restrict__ weights, int top, int width) {
   bw::pdl_enter();
+  constexpr int per = VEC ? 4 : 1;
   const int r = blockIdx.x;
-  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * per;
   if (c >= width) return;
-  float s = 0.0f;
+  float s[4] = {0.0f, 0.0f, 0.0f, 0.0f};
   for (int j = 0; j < top; ++j) {
     const size_t p = static_cast<size_t>(r) * top + j;
-    s = __fmaf_rn(weights[p], y[static_cast<size_t>(place[p]) * width + c], s);
+    const float wj = weights[p];
+    const float* yr = y + static_cast<size_t>(place[p]) * width + c;
+    if constexpr (VEC) {
+      const float4 v = *reinterpret_cast<const float4*>(yr);
+      s[0] = __fmaf_rn(wj, v.x, s[0]), s[1] = __fmaf_rn(wj, v.y, s[1]);
+      s[2] = __fmaf_rn(wj, v.z, s[2]), s[3] = __fmaf_rn(wj, v.w, s[3]);
+    } else {
+      s[0] = __fmaf_rn(wj, yr[0], s[0]);
+    }
   }
   const size_t o = static_cast<size_t>(r) * width + c;
-  if (d) s = __fadd_rn(d[o], s);
-  x[o] = __fadd_rn(x[o], s);
+#pragma unroll
+  for (int e = 0; e < per; ++e) {
+    float v = s[e];
+    if (d) v = __fadd_rn(d[o + e], v);
+    x[o + e] = __fadd_rn(x[o + e], v);
+  }
 }
 
 }  // namespace
@@ -567,13 +610,24 @@ BW_API int BW_FN(gather_rows)(const act_t* x, const int* order, int order_div, a
 BW_API int BW_FN(glu_clamped)(const act_t* gate_up, act_t* out, int n, int inter, float limit, float alpha,
                               cudaStream_t stream) {
   if (n <= 0 || inter <= 0) return 0;
-  bw::launch_pdl(glu_clamped_kernel, dim3(n, (inter + 255) / 256), dim3(256), 0, stream, gate_up, out, inter, limit, alpha);
+  const int per = 16 / static_cast<int>(sizeof(act_t));
+  if (inter % per == 0 && reinterpret_cast<uintptr_t>(gate_up) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0)
+    bw::launch_pdl(glu_clamped_kernel<true>, dim3(n, (inter / per + 127) / 128), dim3(128), 0, stream, gate_up, out, inter,
+                   limit, alpha);
+  else
+    bw::launch_pdl(glu_clamped_kernel<false>, dim3(n, (inter + 255) / 256), dim3(256), 0, stream, gate_up, out, inter, limit,
+                   alpha);
   return bw::launch_status();
 }
 
 BW_API int BW_FN(combine)(float* x, const float* d, const float* y, const int* place, const float* weights, int n,
                           int top, int width, cudaStream_t stream) {
   if (n <= 0 || width <= 0) return 0;
-  bw::launch_pdl(combine_kernel, dim3(n, (width + 255) / 256), dim3(256), 0, stream, x, d, y, place, weights, top, width);
+  if (width % 4 == 0 && reinterpret_cast<uintptr_t>(y) % 16 == 0)
+    bw::launch_pdl(combine_kernel<true>, dim3(n, (width / 4 + 127) / 128), dim3(128), 0, stream, x, d, y, place, weights, top,
+                   width);
+  else
+    bw::launch_pdl(combine_kernel<false>, dim3(n, (width + 255) / 256), dim3(256), 0, stream, x, d, y, place, weights, top,
+                   width);
   return bw::launch_status();
 }
