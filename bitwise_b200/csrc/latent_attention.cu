@@ -340,15 +340,15 @@ latent_attention_tc_kernel(const act_t* __restrict__ q, int q_stride, const act_
     const act_t* src = valid ? q + static_cast<size_t>(row0 + qi / nh) * q_stride + (h0 + qi % nh) * dk + c * 8 : q;
     bw::copy16_async(bw::smem_addr(qs + qi * rs + c * 8), src, valid);
   }
+  // a warp copies whole keys: the page is looked up once per key, the lanes share its 16-byte pieces
   auto load_keys_async = [&](int tile) {
     __nv_bfloat16* dst = ks + (tile & 1) * kTcKeys * rs;
     const int k0 = kbeg + tile * kTcKeys;
-    for (int idx = tid; idx < kTcKeys * pieces; idx += threads) {
-      const int kk = idx / pieces, c = idx - kk * pieces;
+    for (int kk = warp; kk < kTcKeys; kk += 4 * CS) {
       const int kp = k0 + kk;
       const bool valid = kp <= kend;
-      const act_t* src = valid ? cache + (static_cast<size_t>(bt[kp / page]) * page + kp % page) * dk + c * 8 : cache;
-      bw::copy16_async(bw::smem_addr(dst + kk * rs + c * 8), src, valid);
+      const act_t* src = valid ? cache + (static_cast<size_t>(bt[kp / page]) * page + kp % page) * dk : cache;
+      for (int c = lane; c < pieces; c += 32) bw::copy16_async(bw::smem_addr(dst + kk * rs + c * 8), valid ? src + c * 8 : cache, valid);
     }
   };
   if (tiles > 0) load_keys_async(0);
@@ -373,30 +373,58 @@ latent_attention_tc_kernel(const act_t* __restrict__ q, int q_stride, const act_
     float sc[4][4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.0f;
+    // The fragments of step k + 1 are requested before the products of step k are issued, and
+    // even and odd steps add into accumulators of their own (summed at the end), so that neither
+    // the loads nor the chain of dependent products stand in the warp's way.
+    const uint32_t q_at = bw::smem_addr(qs + (wq * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * rs + 8 * (lane >> 4));
+    const uint32_t k_at = bw::smem_addr(kt + ((lane & 7) + 8 * (lane >> 4)) * rs + 8 * ((lane >> 3) & 1));
     if constexpr (CS == 1) {
-      for (int kk = 0; kk < dk; kk += 16) {
-        uint32_t a[4], b0[4], b1[4];
-        bw::ldsm4(a, bw::smem_addr(qs + (wq * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * rs + kk + 8 * (lane >> 4)));
-        bw::ldsm4(b0, bw::smem_addr(kt + ((lane & 7) + 8 * (lane >> 4)) * rs + kk + 8 * ((lane >> 3) & 1)));
-        bw::ldsm4(b1, bw::smem_addr(kt + (16 + (lane & 7) + 8 * (lane >> 4)) * rs + kk + 8 * ((lane >> 3) & 1)));
-        bw::mma16816(sc[0], a, b0[0], b0[1]);
-        bw::mma16816(sc[1], a, b0[2], b0[3]);
-        bw::mma16816(sc[2], a, b1[0], b1[1]);
-        bw::mma16816(sc[3], a, b1[2], b1[3]);
+      float odd[4][4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) odd[j][0] = odd[j][1] = odd[j][2] = odd[j][3] = 0.0f;
+      uint32_t a0[4], b00[4], b01[4], a1[4], b10[4], b11[4];
+      int kk = 0;
+      bw::ldsm4(a0, q_at), bw::ldsm4(b00, k_at), bw::ldsm4(b01, k_at + 16 * rs * 2);
+      for (; kk + 16 < dk; kk += 32) {
+        bw::ldsm4(a1, q_at + (kk + 16) * 2), bw::ldsm4(b10, k_at + (kk + 16) * 2), bw::ldsm4(b11, k_at + (16 * rs + kk + 16) * 2);
+        bw::mma16816(sc[0], a0, b00[0], b00[1]), bw::mma16816(sc[1], a0, b00[2], b00[3]);
+        bw::mma16816(sc[2], a0, b01[0], b01[1]), bw::mma16816(sc[3], a0, b01[2], b01[3]);
+        if (kk + 32 < dk)
+          bw::ldsm4(a0, q_at + (kk + 32) * 2), bw::ldsm4(b00, k_at + (kk + 32) * 2), bw::ldsm4(b01, k_at + (16 * rs + kk + 32) * 2);
+        bw::mma16816(odd[0], a1, b10[0], b10[1]), bw::mma16816(odd[1], a1, b10[2], b10[3]);
+        bw::mma16816(odd[2], a1, b11[0], b11[1]), bw::mma16816(odd[3], a1, b11[2], b11[3]);
       }
+      if (kk < dk) {
+        bw::mma16816(sc[0], a0, b00[0], b00[1]), bw::mma16816(sc[1], a0, b00[2], b00[3]);
+        bw::mma16816(sc[2], a0, b01[0], b01[1]), bw::mma16816(sc[3], a0, b01[2], b01[3]);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) sc[j][e] += odd[j][e];
     } else {
       // each set of warps forms the scores of half of the tile's keys and hands them to the other
-      // through shared memory (a score is one accumulator chain either way)
-      float half[2][4];
+      // through shared memory (a score is the same chain either way)
+      float half[2][4], odd[2][4];
 #pragma unroll
-      for (int j = 0; j < 2; ++j) half[j][0] = half[j][1] = half[j][2] = half[j][3] = 0.0f;
-      for (int kk = 0; kk < dk; kk += 16) {
-        uint32_t a[4], b[4];
-        bw::ldsm4(a, bw::smem_addr(qs + (wq * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * rs + kk + 8 * (lane >> 4)));
-        bw::ldsm4(b, bw::smem_addr(kt + (16 * cs + (lane & 7) + 8 * (lane >> 4)) * rs + kk + 8 * ((lane >> 3) & 1)));
-        bw::mma16816(half[0], a, b[0], b[1]);
-        bw::mma16816(half[1], a, b[2], b[3]);
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) half[j][e] = odd[j][e] = 0.0f;
+      const uint32_t kh_at = k_at + 16 * cs * rs * 2;
+      uint32_t a0[4], b0[4], a1[4], b1[4];
+      int kk = 0;
+      bw::ldsm4(a0, q_at), bw::ldsm4(b0, kh_at);
+      for (; kk + 16 < dk; kk += 32) {
+        bw::ldsm4(a1, q_at + (kk + 16) * 2), bw::ldsm4(b1, kh_at + (kk + 16) * 2);
+        bw::mma16816(half[0], a0, b0[0], b0[1]), bw::mma16816(half[1], a0, b0[2], b0[3]);
+        if (kk + 32 < dk) bw::ldsm4(a0, q_at + (kk + 32) * 2), bw::ldsm4(b0, kh_at + (kk + 32) * 2);
+        bw::mma16816(odd[0], a1, b1[0], b1[1]), bw::mma16816(odd[1], a1, b1[2], b1[3]);
       }
+      if (kk < dk) bw::mma16816(half[0], a0, b0[0], b0[1]), bw::mma16816(half[1], a0, b0[2], b0[3]);
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) half[j][e] += odd[j][e];
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
         float* dst = ss + qa * kScoreRow + 16 * cs + 8 * j + 2 * (lane & 3);
@@ -437,8 +465,11 @@ latent_attention_tc_kernel(const act_t* __restrict__ q, int q_stride, const act_
         ra += sc[j][e], rb += sc[j][2 + e];
       }
     suma = __fmaf_rn(suma, alpha_a, ra), sumb = __fmaf_rn(sumb, alpha_b, rb);
+    // once a row's maximum stands, its factor is 1: most tiles rescale nothing
+    if (__any_sync(0xffffffffu, alpha_a != 1.0f || alpha_b != 1.0f)) {
 #pragma unroll
-    for (int i = 0; i < NT; ++i) acc[i][0] *= alpha_a, acc[i][1] *= alpha_a, acc[i][2] *= alpha_b, acc[i][3] *= alpha_b;
+      for (int i = 0; i < NT; ++i) acc[i][0] *= alpha_a, acc[i][1] *= alpha_a, acc[i][2] *= alpha_b, acc[i][3] *= alpha_b;
+    }
 #pragma unroll
     for (int k2 = 0; k2 < 2; ++k2) {
       uint32_t hi[4], lo[4];
@@ -449,17 +480,29 @@ latent_attention_tc_kernel(const act_t* __restrict__ q, int q_stride, const act_
         hi[f] = bw::pack_bf16(v0, v1);
         lo[f] = bw::pack_bf16(v0 - __bfloat162float(h0b), v1 - __bfloat162float(h1b));
       }
+      const uint32_t v_at = bw::smem_addr(kt + (k2 * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * rs + 8 * (lane >> 4));
 #pragma unroll
-      for (int np = 0; np < NT / 2; ++np) {
-        const int d0 = (cs * NT + 2 * np) * 8;
-        if (d0 < rank) {
-          uint32_t b[4];
-          bw::ldsm4_trans(b, bw::smem_addr(kt + (k2 * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * rs + d0 + 8 * (lane >> 4)));
-          bw::mma16816(acc[2 * np], hi, b[0], b[1]);
-          bw::mma16816(acc[2 * np], lo, b[0], b[1]);
-          bw::mma16816(acc[2 * np + 1], hi, b[2], b[3]);
-          bw::mma16816(acc[2 * np + 1], lo, b[2], b[3]);
+      for (int n4 = 0; n4 < NT / 2; n4 += 4) {
+        // four fragments of latents are requested, then their products follow, the high parts of
+        // the weights first: no product waits for the one before it on the same accumulator
+        uint32_t b[4][4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int d0 = (cs * NT + 2 * (n4 + u)) * 8;
+          if (d0 < rank) bw::ldsm4_trans(b[u], v_at + d0 * 2);
         }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if ((cs * NT + 2 * (n4 + u)) * 8 < rank) {
+            bw::mma16816(acc[2 * (n4 + u)], hi, b[u][0], b[u][1]);
+            bw::mma16816(acc[2 * (n4 + u) + 1], hi, b[u][2], b[u][3]);
+          }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if ((cs * NT + 2 * (n4 + u)) * 8 < rank) {
+            bw::mma16816(acc[2 * (n4 + u)], lo, b[u][0], b[u][1]);
+            bw::mma16816(acc[2 * (n4 + u) + 1], lo, b[u][2], b[u][3]);
+          }
       }
     }
     __syncthreads();
