@@ -97,7 +97,7 @@ def test_layernorm(dtype, width):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("rank,rot_dim,dims", [(40, 8, 8), (33, 6, 4), (136, 4, 4), (96, 32, 0)])
+@pytest.mark.parametrize("rank,rot_dim,dims", [(40, 8, 8), (33, 6, 4), (136, 4, 4), (104, 24, 0)])
 def test_latent_store_and_query_rotation(dtype, rank, rot_dim, dims):
     from bitwise_b200.parts.rope import RotaryEncoding
     ops = ops_of(dtype)
@@ -201,7 +201,7 @@ def _attention_case_once(dtype, heads, rank, rot_dim, seqs, spike=None, window=0
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("heads,rank,rot_dim", [(3, 40, 8), (1, 33, 6), (40, 136, 4), (8, 96, 16), (5, 300, 20),
+@pytest.mark.parametrize("heads,rank,rot_dim", [(3, 40, 8), (1, 33, 6), (40, 136, 4), (8, 88, 24), (5, 300, 20),
                                                 (70, 64, 16), (6, 264, 24), (2, 512, 64)])
 def test_latent_attention_tiles(dtype, heads, rank, rot_dim):
     # portions that begin in the middle of a page and of a key tile, single rows beside them,
@@ -237,7 +237,7 @@ def test_latent_attention_window(dtype):
 
 
 @pytest.mark.parametrize("experts,groups,keep,top", [(8, 4, 2, 3), (6, 1, 1, 2), (5, 1, 1, 1), (6, 6, 3, 2), (64, 8, 3, 6),
-                                                     (12, 4, 3, 3), (12, 4, 4, 5)])
+                                                     (15, 5, 3, 4), (12, 4, 4, 5)])
 def test_route(experts, groups, keep, top):
     ops = ops_of("float32")
     g = torch.Generator().manual_seed(experts)
@@ -355,7 +355,7 @@ def row_errors(got, want):
     return np.sqrt(((got - want) ** 2).mean(-1)) / np.sqrt((want ** 2).mean(-1))
 
 
-def judge(errors, dtype, what):
+def assess(errors, dtype, what):
     """float32: every position within the tolerance.  bfloat16: rounding now and then turns a
     close call of a router (another expert, a step in the output), so the bound is on the mean
     and on the share of positions that are far off."""
@@ -374,7 +374,7 @@ def compare(name, dtype, got_by_request):
         got = got_by_request[rid]
         assert got.shape == want.shape
         errors.append(row_errors(got, want))
-    judge(errors, dtype, f"{name} {dtype} against the plain implementation")
+    assess(errors, dtype, f"{name} {dtype} against the plain implementation")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -400,7 +400,7 @@ def test_whole_prompts_and_layers(name, dtype):
         for b in model.decoder.blocks:
             del b.forward
     for i, (got, w) in enumerate(zip(seen, want)):
-        judge([row_errors(got.float().cpu().numpy(), w.numpy())], dtype, f"stream after layer {i}")
+        assess([row_errors(got.float().cpu().numpy(), w.numpy())], dtype, f"stream after layer {i}")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -418,7 +418,7 @@ def test_every_cut_gives_the_same_logits(name, dtype):
             got = R.collect(steps, R.run_in_process(model, steps, pool, use_graphs=graphs), vocab)
             compare(name, dtype, got)
             # between two cuts only rounding differs: far less than between precision and plain
-            judge([row_errors(got[rid], base[rid]) for rid in reqs], dtype, f"{name} {dtype} {pname} against whole prompts")
+            assess([row_errors(got[rid], base[rid]) for rid in reqs], dtype, f"{name} {dtype} {pname} against whole prompts")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -457,7 +457,7 @@ def test_long_decoding_over_reused_pages(dtype):
     assert not queue
     stepper.finish("long")
     assert stepper.manager.all_free()
-    judge(errors, dtype, "long decoding")
+    assess(errors, dtype, "long decoding")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
