@@ -43,7 +43,9 @@ class CacheStorage:
                 pages = pages_per_group[self.group_of_entry[e]]
                 shape = (max(pages, 1) + 1, need.kv_heads, page_size, need.head_dim)
                 self.k[e] = torch.zeros(shape, dtype=dtype, device=device)
-                self.v[e] = torch.zeros(shape, dtype=dtype, device=device)
+                v_dim = need.head_dim if need.v_dim is None else need.v_dim
+                if v_dim:  # 0: the mixer's values are its keys, nothing more is kept
+                    self.v[e] = torch.zeros(shape[:3] + (v_dim,), dtype=dtype, device=device)
             elif isinstance(need, PagedLatentNeed):
                 # one tensor holds the latent and the shared rotated key part of a position
                 pages = pages_per_group[self.group_of_entry[e]]

@@ -65,3 +65,5 @@ def _ensure_builtin() -> None:
         from ..models import llama  # noqa: F401  (registers itself on import)
     if "Nuderax" not in _ARCHITECTURES:
         from ..models import nuderax  # noqa: F401
+    if "Favudra" not in _ARCHITECTURES:
+        from ..models import favudra  # noqa: F401

@@ -93,22 +93,23 @@ BW_API int bw_selftest_bounded_wait(unsigned polls, int* result, cudaStream_t st
 
 template <typename T>
 __global__ void embed_rows_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
-                                  float* __restrict__ out, int n, int width) {
+                                  float* __restrict__ out, int n, int width, float scale) {
   bw::pdl_enter();
   const int r = blockIdx.x;
   const T* src = table + static_cast<size_t>(tokens[r]) * width;
   float* dst = out + static_cast<size_t>(r) * width;
-  for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = static_cast<float>(src[i]);
+  for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = __fmul_rn(static_cast<float>(src[i]), scale);
 }
 
+// out[r] = table[tokens[r]] * scale in float32 (scale 1 for models that embed unscaled: exact).
 BW_API int bw_embed_rows(const void* table, int table_is_bf16, const int* tokens, float* out, int n,
-                         int width, cudaStream_t stream) {
+                         int width, float scale, cudaStream_t stream) {
   if (n <= 0) return 0;
   const int threads = width >= 1024 ? 256 : 128;
   if (table_is_bf16)
-    bw::launch_pdl(embed_rows_kernel<__nv_bfloat16>, dim3(n), dim3(threads), 0, stream, static_cast<const __nv_bfloat16*>(table), tokens, out, n, width);
+    bw::launch_pdl(embed_rows_kernel<__nv_bfloat16>, dim3(n), dim3(threads), 0, stream, static_cast<const __nv_bfloat16*>(table), tokens, out, n, width, scale);
   else
-    bw::launch_pdl(embed_rows_kernel<float>, dim3(n), dim3(threads), 0, stream, static_cast<const float*>(table), tokens, out, n, width);
+    bw::launch_pdl(embed_rows_kernel<float>, dim3(n), dim3(threads), 0, stream, static_cast<const float*>(table), tokens, out, n, width, scale);
   return bw::launch_status();
 }
 

@@ -1,0 +1,40 @@
+// The norm that follows a sublayer in blocks with a norm on both sides of each sublayer:
+// x += d / sqrt(mean(d^2) + eps) * w, with d the sublayer's output (float32) and x the float32
+// stream. One block per row; the sum of squares is formed in an order that depends on the width
+// only, and the residual sum is float32 in both precisions.
+#include "bw_act.cuh"
+
+namespace {
+
+constexpr int kThreads = 256;
+
+__global__ void __launch_bounds__(kThreads)
+rmsnorm_residual_kernel(const float* __restrict__ d, const float* __restrict__ w, float* x, int width, float eps) {
+  bw::pdl_enter();
+  extern __shared__ float row[];
+  __shared__ float red[32];
+  const size_t base = static_cast<size_t>(blockIdx.x) * width;
+  float ss = 0.0f;
+  for (int i = threadIdx.x; i < width; i += kThreads) {
+    const float v = d[base + i];
+    row[i] = v;
+    ss = __fmaf_rn(v, v, ss);
+  }
+  const float inv = bw::rms_scale(bw::block_sum(ss, red), width, eps);
+  for (int i = threadIdx.x; i < width; i += kThreads)
+    x[base + i] = __fadd_rn(x[base + i], bw::rms_apply(row[i], inv, w[i]));
+}
+
+}  // namespace
+
+BW_API int BW_FN(rmsnorm_residual)(const float* d, const float* w, float* x, int n, int width, float eps,
+                                   cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (width <= 0 || width > 48 * 1024 / 4) {
+    bw::set_error("rmsnorm_residual: width %d (1 .. 12288)", width);
+    return -1;
+  }
+  bw::launch_pdl(rmsnorm_residual_kernel, dim3(n), dim3(kThreads), static_cast<size_t>(width) * sizeof(float), stream, d,
+                 w, x, width, eps);
+  return bw::launch_status();
+}

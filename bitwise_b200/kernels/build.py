@@ -38,6 +38,11 @@ KERNEL_SETS: Dict[str, List[tuple]] = {
                   ("routed_ffn.cu", ["-DBW_ACT_BF16=0"])],
     "bf16_parts": [("common.cu", []), ("layer_norm.cu", ["-DBW_ACT_BF16=1"]), ("latent_attention.cu", ["-DBW_ACT_BF16=1"]),
                    ("routed_ffn.cu", ["-DBW_ACT_BF16=1"])],
+    # mixers with a convolution's or a recurrence's state, and the norm after a sublayer
+    "f32_mixers": [("common.cu", []), ("sublayer_norm.cu", ["-DBW_ACT_BF16=0"]), ("scored_attention.cu", ["-DBW_ACT_BF16=0"]),
+                   ("linear_recurrence.cu", ["-DBW_ACT_BF16=0"])],
+    "bf16_mixers": [("common.cu", []), ("sublayer_norm.cu", ["-DBW_ACT_BF16=1"]), ("scored_attention.cu", ["-DBW_ACT_BF16=1"]),
+                    ("linear_recurrence.cu", ["-DBW_ACT_BF16=1"])],
 }
 
 # head sizes whose attention library a full build prepares (others are compiled when a model asks)
@@ -215,6 +220,6 @@ def ensure_host_built(verbose: bool = True) -> str:
 def build_all(verbose: bool = True) -> List[str]:
     """Compile every kernel set (what a 'does it build' check wants)."""
     out = [ensure_host_built(verbose)]
-    out += [ensure_built(k, (), verbose) for k in ("f32", "bf16", "f32_parts", "bf16_parts")]
+    out += [ensure_built(k, (), verbose) for k in ("f32", "bf16", "f32_parts", "bf16_parts", "f32_mixers", "bf16_mixers")]
     out += [ensure_built("bf16_attn", (f"BW_HEAD_DIM={hd}",), verbose) for hd in DEFAULT_HEAD_DIMS]
     return out

@@ -119,8 +119,8 @@ class KernelOps:
         self.launches += launches
 
     # -- shared kernels ----------------------------------------------------------------
-    def embed_rows(self, table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor) -> None:
-        """out[r] = table[tokens[r]] widened to float32."""
+    def embed_rows(self, table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> None:
+        """out[r] = table[tokens[r]] widened to float32, times ``scale``."""
         n, width = out.shape
         _need(tokens, torch.int32, "embed_rows tokens")
         _need(out, torch.float32, "embed_rows out", 2)
@@ -128,7 +128,7 @@ class KernelOps:
             raise KernelError("embed_rows: table must be float32 or bfloat16 of the output's width")
         _need(table, table.dtype, "embed_rows table", 2)
         self._call("bw_embed_rows", _p(table), _c_int(int(table.dtype == torch.bfloat16)), _p(tokens), _p(out),
-                   _c_int(n), _c_int(width), self._stream())
+                   _c_int(n), _c_int(width), _c_float(scale), self._stream())
 
     def patch_tokens(self, tokens: torch.Tensor, rows: torch.Tensor, src: torch.Tensor, values: torch.Tensor,
                      count: int) -> None:
@@ -308,7 +308,7 @@ class KernelOps:
             dev = torch.device("cuda", self._device_index())
             self._failure_word = torch.zeros(1, dtype=torch.int32, device=dev)
             self._failure_host = torch.zeros(1, dtype=torch.int32, pin_memory=True)
-            for lib in [self.lib] + list(self._attn_libs.values()) + [l for l in [getattr(self, "_parts", None)] if l]:
+            for lib in [self.lib] + list(self._attn_libs.values()) + [l for l in [getattr(self, "_parts", None), getattr(self, "_mixers", None)] if l]:
                 lib.bw_set_failure_word(_p(self._failure_word))
         return self._failure_word, self._failure_host
 
@@ -887,6 +887,164 @@ class KernelOps:
             raise KernelError("combine: shapes differ")
         self._pcall("combine", _p(x), _p(d), _p(y), _p(place), _p(weights), _c_int(n), _c_int(top), _c_int(width),
                     self._stream())
+
+    # -- mixers with state beside or instead of pages, and the norm after a sublayer (their library
+    #    is loaded at first use) -------------------------------------------------------------------
+    def _mixers_lib(self):
+        lib = getattr(self, "_mixers", None)
+        if lib is None:
+            path = build.ensure_built(f"{self.kind}_mixers", (), self._verbose_build)
+            try:
+                lib = ctypes.CDLL(path)
+            except OSError as e:
+                raise KernelError(f"cannot load the kernel library {path}: {e}") from None
+            lib.bw_last_error.restype = ctypes.c_char_p
+            if self._failure_word is not None:
+                lib.bw_set_failure_word(_p(self._failure_word))
+            self._mixers = lib
+            self._mixers_fns = {}
+        return lib
+
+    def _mcall(self, name: str, *args, launches: int = 1) -> None:
+        lib = self._mixers_lib()
+        fn = self._mixers_fns.get(name)
+        if fn is None:
+            fn = getattr(lib, f"bw_{self.kind}_{name}")
+            fn.restype = _c_int
+            self._mixers_fns[name] = fn
+        rc = fn(*args)
+        if rc != 0:
+            raise KernelError(f"{name} failed ({rc}): " + lib.bw_last_error().decode("utf-8", "replace"))
+        self.launches += launches
+
+    def rmsnorm_residual(self, d: torch.Tensor, weight: torch.Tensor, eps: float, x: torch.Tensor) -> None:
+        """x[r] += d[r] / sqrt(mean(d[r]^2) + eps) * weight; d, weight and x float32."""
+        n, width = x.shape
+        _need(d, torch.float32, "rmsnorm_residual d", 2)
+        _need(x, torch.float32, "rmsnorm_residual x", 2)
+        _need(weight, torch.float32, "rmsnorm_residual weight", 1)
+        if tuple(d.shape) != (n, width) or weight.shape[0] != width:
+            raise KernelError("rmsnorm_residual: shapes differ")
+        self._mcall("rmsnorm_residual", _p(d), _p(weight), _p(x), _c_int(n), _c_int(width), _c_float(eps), self._stream())
+
+    def scored_attention_tile_heights(self, group: int, dim: int, vdim: int):
+        """The heights of query tiles (rows of one sequence per thread block) that ``scored_attention``
+        wants prepared for ``group`` query heads on a key/value head."""
+        fn = getattr(self._mixers_lib(), f"bw_{self.kind}_scored_attention_tile_rows")
+        return [int(fn(_c_int(group)))]
+
+    def qkv_prepare(self, u: torch.Tensor, conv_w: Optional[torch.Tensor], conv_state: Optional[torch.Tensor],
+                    q_norm: Optional[torch.Tensor], k_norm: Optional[torch.Tensor], eps: float,
+                    cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], batch, block_table: torch.Tensor,
+                    kcache: torch.Tensor, vcache: Optional[torch.Tensor], q_out: torch.Tensor, heads: int,
+                    write_kv_heads: int, dim: int, vdim: int) -> None:
+        """From the projected rows ``u`` (float32 [n, cols]: ``heads`` query heads of ``dim``, then, when
+        ``write_kv_heads`` > 0, that many key heads of ``dim`` and, with ``vcache``, value heads of
+        ``vdim``): the convolution over time with ``conv_w`` [cols, taps] (inputs before the step's
+        first row of a sequence from ``conv_state`` [slots, taps - 1, cols], zeros before position 0),
+        the norm per head of q and k with ``q_norm`` / ``k_norm`` [dim], the rotation of the first 2 *
+        pairs entries of q and k by the tables' row of the position; q into ``q_out`` [n, heads * dim],
+        keys and values into their pages.  Each step may be absent (None)."""
+        n, cols = u.shape
+        _need(u, torch.float32, "qkv_prepare u", 2)
+        _need(q_out, self.act_dtype, "qkv_prepare q_out", 2)
+        _need(block_table, torch.int32, "qkv_prepare block_table", 2)
+        _need(kcache, self.act_dtype, "qkv_prepare kcache", 4)
+        taps = 0
+        if conv_w is not None:
+            _need(conv_w, torch.float32, "qkv_prepare conv_w", 2)
+            taps = conv_w.shape[1]
+            if conv_w.shape[0] != cols:
+                raise KernelError("qkv_prepare: one row of taps per channel is needed")
+        if conv_state is not None:
+            _need(conv_state, torch.float32, "qkv_prepare conv_state", 3)
+            if tuple(conv_state.shape[1:]) != (taps - 1, cols):
+                raise KernelError("qkv_prepare: the state is not [slots, taps - 1, cols]")
+        for w_, what in ((q_norm, "q_norm"), (k_norm, "k_norm")):
+            if w_ is not None:
+                _need(w_, torch.float32, "qkv_prepare " + what, 1)
+                if w_.shape[0] != dim:
+                    raise KernelError("qkv_prepare: a norm weight is not of the head's size")
+        pairs = self._check_tables(cos, sin, dim, "qkv_prepare")
+        want = heads * dim + write_kv_heads * dim + (write_kv_heads * vdim if vcache is not None else 0)
+        if cols != want or tuple(q_out.shape) != (n, heads * dim):
+            raise KernelError(f"qkv_prepare: rows of {cols} columns do not hold {want}")
+        if write_kv_heads and (tuple(kcache.shape[1:]) != (write_kv_heads, kcache.shape[2], dim)):
+            raise KernelError("qkv_prepare: key cache is not [pages, kv_heads, page, dim]")
+        if vcache is not None:
+            _need(vcache, self.act_dtype, "qkv_prepare vcache", 4)
+            if write_kv_heads and tuple(vcache.shape[1:]) != (write_kv_heads, kcache.shape[2], vdim):
+                raise KernelError("qkv_prepare: value cache is not [pages, kv_heads, page, vdim]")
+        self._mcall("qkv_prepare", _p(u), _c_int(cols), _p(conv_w), _c_int(taps), _p(conv_state), _p(q_norm), _p(k_norm),
+                    _c_float(eps), _p(cos), _p(sin), _c_int(pairs), _p(batch.pos), _p(batch.row_seq), _p(batch.seq_row0),
+                    _p(batch.seq_pos0), _p(batch.seq_slot), _p(block_table), _c_int(block_table.shape[1]), _p(kcache),
+                    _p(vcache if write_kv_heads else None), _p(q_out), _c_int(n), _c_int(heads), _c_int(write_kv_heads),
+                    _c_int(dim), _c_int(vdim), _c_int(kcache.shape[2]), self._stream())
+
+    def conv_state_update(self, u: torch.Tensor, state: torch.Tensor, batch, taps: int, seq_tiles) -> None:
+        """state[slot of s][i] = the projected row of position end_s - (taps - 1) + i for every sequence s
+        of the step (``seq_tiles``: one tile per sequence), end_s its length after the step: from the
+        step's rows ``u``, from the old state, or zero before position 0."""
+        _need(u, torch.float32, "conv_state_update u", 2)
+        _need(state, torch.float32, "conv_state_update state", 3)
+        t_seq, t_row0, t_rows, t_count = seq_tiles
+        if tuple(state.shape[1:]) != (taps - 1, u.shape[1]):
+            raise KernelError("conv_state_update: the state is not [slots, taps - 1, cols]")
+        self._mcall("conv_state_update", _p(u), _c_int(u.shape[1]), _p(state), _c_int(taps), _p(t_seq), _p(t_row0),
+                    _p(t_rows), _c_int(t_count), _p(batch.seq_pos0), _p(batch.seq_slot), self._stream())
+
+    def scored_attention(self, q: torch.Tensor, kcache: torch.Tensor, vcache: Optional[torch.Tensor],
+                         block_table: torch.Tensor, out: torch.Tensor, heads: int, kv_heads: int, dim: int, vdim: int,
+                         scale: float, softcap: float, sink: bool, slopes: Optional[torch.Tensor], window: int,
+                         batch) -> None:
+        """out[r, h] = sum_j p_j v_j over the cached positions j <= pos[r] of row r's sequence (from pos -
+        window + 1 on when window > 0) with s_j = (q[r, h] . k_j) * scale, then s_j <- softcap * tanh(s_j /
+        softcap) when softcap > 0, then s_j <- s_j - slopes[h] * (pos[r] - j) when slopes are given, and
+        p_j = exp(s_j) / (sum exp(s) + (1 if sink else 0)).  ``vcache`` None: the values are the keys."""
+        n = q.shape[0]
+        _need(q, self.act_dtype, "scored_attention q", 2)
+        _need(out, self.act_dtype, "scored_attention out", 2)
+        _need(kcache, self.act_dtype, "scored_attention kcache", 4)
+        _need(block_table, torch.int32, "scored_attention block_table", 2)
+        if vcache is not None:
+            _need(vcache, self.act_dtype, "scored_attention vcache", 4)
+        elif vdim != dim:
+            raise KernelError("scored_attention: values that are the keys have the keys' size")
+        if slopes is not None:
+            _need(slopes, torch.float32, "scored_attention slopes", 1)
+            if slopes.shape[0] != heads:
+                raise KernelError("scored_attention: one slope per head is needed")
+        if q.shape[1] != heads * dim or tuple(out.shape) != (n, heads * vdim) or kcache.shape[1] != kv_heads or \
+                kcache.shape[3] != dim:
+            raise KernelError("scored_attention: shapes do not fit the heads")
+        t_seq, t_row0, t_rows, t_count = batch.query_tiles(self.scored_attention_tile_heights(heads // kv_heads, dim, vdim)[0])
+        self._mcall("scored_attention", _p(q), _c_int(q.shape[1]), _p(kcache), _p(vcache), _p(block_table),
+                    _c_int(block_table.shape[1]), _p(t_seq), _p(t_row0), _p(t_rows), _c_int(t_count), _p(batch.seq_pos0),
+                    _p(batch.seq_row0), _p(out), _c_int(out.shape[1]), _c_int(heads), _c_int(kv_heads), _c_int(dim),
+                    _c_int(vdim), _c_int(kcache.shape[2]), _c_float(scale), _c_float(softcap), _c_int(int(bool(sink))),
+                    _p(slopes), _c_int(window), self._stream())
+
+    def gla_scan(self, u: torch.Tensor, z: torch.Tensor, bias: torch.Tensor, tau: float, state: torch.Tensor,
+                 norm_w: torch.Tensor, eps: float, out: torch.Tensor, heads: int, dim: int, vdim: int, q_scale: float,
+                 batch, seq_tiles) -> None:
+        """The recurrence S_t = diag(a_t) S_(t-1) + k_t v_t^T, o_t = S_t^T (q_t * q_scale) per head over the
+        rows of every sequence of the step (``seq_tiles``: one tile per sequence), from and into ``state``
+        [slots, heads, dim, vdim] (zero at a request's first position), with a = sigmoid(z + bias) ** (1 /
+        tau); out = o / rms(o) * norm_w * silu(gate).  ``u`` (float32) holds q | k | v | gate per row."""
+        n = u.shape[0]
+        _need(u, torch.float32, "gla_scan u", 2)
+        _need(z, torch.float32, "gla_scan z", 2)
+        _need(bias, torch.float32, "gla_scan bias", 1)
+        _need(state, torch.float32, "gla_scan state", 4)
+        _need(norm_w, torch.float32, "gla_scan norm_w", 1)
+        _need(out, self.act_dtype, "gla_scan out", 2)
+        if u.shape[1] != 2 * heads * (dim + vdim) or tuple(z.shape) != (n, heads * dim) or bias.shape[0] != heads * dim or \
+                tuple(state.shape[1:]) != (heads, dim, vdim) or norm_w.shape[0] != vdim or tuple(out.shape) != (n, heads * vdim):
+            raise KernelError("gla_scan: shapes do not fit the heads")
+        t_seq, t_row0, t_rows, t_count = seq_tiles
+        self._mcall("gla_scan", _p(u), _c_int(u.shape[1]), _p(z), _p(bias), _c_float(tau), _p(state), _p(norm_w),
+                    _c_float(eps), _p(out), _p(t_seq), _p(t_row0), _p(t_rows), _c_int(t_count), _p(batch.seq_pos0),
+                    _p(batch.seq_slot), _c_int(heads), _c_int(dim), _c_int(vdim), _c_float(q_scale), self._stream())
 
 
 _OPS = {}

@@ -21,6 +21,7 @@ from .config.registry import architecture_of, config_from_folder, lookup_archite
 from .engine.step import StepEntry, Stepper
 from .weights.loader import KEEP32, load_state, state_from_tensors
 from .weights.random_init import random_tensors, write_model_folder
+from .weights.safetensors_io import open_model_shards
 
 _TORCH_DTYPE = {"float32": torch.float32, "bfloat16": torch.bfloat16}
 _ALIASES = {"fp32": "float32", "f32": "float32", "float32": "float32", "bf16": "bfloat16", "bfloat16": "bfloat16"}
@@ -52,6 +53,11 @@ class Model:
         config.json's ``architectures``."""
         dtype = normalize_dtype(dtype)
         arch, config = config_from_folder(folder)
+        if hasattr(config, "with_tensor_shapes"):  # sizes that only the stored tensors give
+            shards = open_model_shards(folder)
+            config = config.with_tensor_shapes({n: tuple(sh.entries[n].shape) for sh in shards for n in sh.names()})
+            for sh in shards:
+                sh.close()
         decoder = arch.build(config)
         ops = ops or _default_ops(dtype)
         state = load_state(folder, decoder.param_specs(), _TORCH_DTYPE[dtype], device,
@@ -78,8 +84,9 @@ class Model:
             gen.manual_seed(seed)
             state = {}
             for s in specs:
-                if s.init == "ones":
-                    state[s.name] = torch.ones(s.shape, dtype=torch.float32, device=device)
+                if s.init in ("ones", "zeros"):
+                    state[s.name] = torch.full(s.shape, 1.0 if s.init == "ones" else 0.0, dtype=torch.float32,
+                                               device=device)
                 else:
                     t = torch.empty(s.shape, dtype=torch.float32, device=device)
                     t.normal_(0.0, std, generator=gen)
@@ -98,6 +105,8 @@ class Model:
         architecture declares like a checkpoint read from a folder."""
         dtype = normalize_dtype(dtype)
         arch = lookup_architecture(config.architectures[0])
+        if hasattr(config, "with_tensor_shapes"):
+            config = config.with_tensor_shapes({n: tuple(t.shape) for n, t in tensors.items()})
         decoder = arch.build(config)
         ops = ops or _default_ops(dtype)
         state = state_from_tensors(tensors, decoder.param_specs(), _TORCH_DTYPE[dtype], device,

@@ -1,5 +1,6 @@
 from .decoder import DecoderModel, LayerRun, sequential_schedule
 from . import llama  # noqa: F401  (registers LlamaForCausalLM)
 from . import nuderax  # noqa: F401  (registers Nuderax)
+from . import favudra  # noqa: F401  (registers Favudra)
 
 __all__ = ["DecoderModel", "LayerRun", "sequential_schedule"]

@@ -24,6 +24,7 @@ class LayerRun:
     block: int   # index into DecoderModel.blocks
     cache: int   # index of the cache entry this run uses
     owns_cache: bool = True  # False: reads an entry that another run writes
+    state: Optional[int] = None  # a second entry of the run's own: the slot state its mixer wants beside ``cache``
 
 
 def sequential_schedule(num_layers: int) -> List[LayerRun]:
@@ -63,6 +64,14 @@ class DecoderModel:
                 b = self.blocks[run.block].cache_need()
                 if a != b:
                     raise ValueError(f"run {i} reads a cache of another shape ({b} vs {a})")
+        for i, run in enumerate(self.schedule):
+            need = getattr(self.blocks[run.block], "state_need", lambda: None)()
+            if (run.state is None) != (need is None):
+                raise ValueError(f"run {i}: the block {'wants' if need is not None else 'has no use for'} a state entry")
+            if run.state is not None:
+                if run.state in owners:
+                    raise ValueError(f"cache entry {run.state} is owned by runs {owners[run.state]} and {i}")
+                owners[run.state] = i
         self.cache_entries = sorted(owners)
         if self.cache_entries != list(range(len(self.cache_entries))):
             raise ValueError("cache entries must be numbered 0..n-1 without gaps")
@@ -74,6 +83,8 @@ class DecoderModel:
         for run in self.schedule:
             if run.owns_cache:
                 needs[run.cache] = self.blocks[run.block].cache_need()
+            if run.state is not None:
+                needs[run.state] = self.blocks[run.block].state_need()
         return needs
 
     # -- parameters --------------------------------------------------------------------
@@ -103,7 +114,7 @@ class DecoderModel:
     def tensor_aliases(self) -> Dict[str, str]:
         """Stored name -> declared tensor it must repeat: a tied head stored a second time."""
         if self.head.tied_to is not None:
-            return {f"{self.head.head_name}.weight": self.head.tied_to.tensor_name(self.embed_prefix)}
+            return {f"{self.head.head_name}{getattr(self.head, 'suffix', '.weight')}": self.head.tied_to.tensor_name(self.embed_prefix)}
         return {}
 
     def prepare(self, ops) -> None:
@@ -121,7 +132,8 @@ class DecoderModel:
         can be captured into a CUDA graph and replayed for steps with the same sizes."""
         parts = [self.embedding, self.head, self.head.norm] + list(self.position_encodings)
         for b in self.blocks:
-            parts += [b, b.mixer, b.feed_forward, b.mixer_norm, b.ffn_norm]
+            parts += [b, b.mixer, b.feed_forward, b.mixer_norm, b.ffn_norm, getattr(b, "mixer_post", None),
+                      getattr(b, "ffn_post", None)]
         return all(getattr(p, "graph_safe", False) for p in parts if p is not None)
 
     def reserve_positions(self, positions: int) -> None:
@@ -141,5 +153,7 @@ class DecoderModel:
             view = cache_views[run.cache]
             if not run.owns_cache and hasattr(view, "writable"):
                 view = type(view)(**{**view.__dict__, "writable": False})
+            if run.state is not None:
+                view = type(view)(**{**view.__dict__, "state": cache_views[run.state]})
             self.blocks[run.block].forward(ctx, x, view)
         return self.head.forward(ctx, x)

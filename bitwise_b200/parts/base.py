@@ -26,10 +26,13 @@ from ..weights.loader import ParamSpec
 @dataclass(frozen=True)
 class PagedKVNeed:
     """Keys and values that grow with the position, kept in pages.
-    ``window`` = None keeps every key; an integer keeps the last ``window`` positions."""
+    ``window`` = None keeps every key; an integer keeps the last ``window`` positions.
+    ``v_dim``: the size of a value where it differs from a key's (None: ``head_dim``); 0 keeps no
+    values at all (a mixer whose values are its keys)."""
     kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    v_dim: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -58,10 +61,11 @@ class SlotStateNeed:
 class PagedKVView:
     """The cache of one layer run, as a mixer sees it during a step."""
     k: torch.Tensor            # [pages, kv_heads, page, head_dim]
-    v: torch.Tensor
+    v: Optional[torch.Tensor]  # [pages, kv_heads, page, v_dim]; None where no values are kept
     block_table: torch.Tensor  # int32 [step sequences, max blocks] of the layer's group
     page_size: int
     writable: bool = True      # False: the run reads another run's cache and stores nothing
+    state: Optional["SlotStateView"] = None  # the run's own slot state beside the pages (Mixer.state_need)
 
 
 @dataclass
@@ -201,6 +205,13 @@ class Mixer(Part):
     """Mixes information between the positions of a sequence."""
 
     def cache_need(self):
+        return None
+
+    def state_need(self):
+        """A :class:`SlotStateNeed` that the mixer wants BESIDE its ``cache_need`` (a paged cache and
+        a little state per request, as a convolution's last inputs), or None.  Every run of the
+        mixer owns such state itself, also a run that reads another run's pages; it arrives as
+        the ``state`` field of the run's cache view."""
         return None
 
     def forward(self, ctx: StepContext, xn: torch.Tensor, x: torch.Tensor, cache) -> None:

@@ -45,6 +45,9 @@ class PreNormBlock(Part):
     def cache_need(self):
         return self.mixer.cache_need()
 
+    def state_need(self):
+        return self.mixer.state_need()
+
     def prepare(self, ops) -> None:
         for part, _ in self._children(""):
             part.prepare(ops)
@@ -90,3 +93,34 @@ class ParallelBlock(PreNormBlock):
         else:
             self.feed_forward.forward(ctx, xn2, delta)
             ctx.ops.add_rows(x, delta)
+
+
+class SandwichBlock(PreNormBlock):
+    """A norm before and after each sublayer: ``x += norm1b(mixer(norm1(x)))``, then ``x +=
+    norm2b(feed_forward(norm2(x)))``.  A sublayer writes its output into a float32 buffer; the
+    norm after it reads that buffer and adds the normed rows to the stream in one kernel
+    (``Norm.forward_residual``).  ``feed_forward`` None: the layer is its mixer alone, with the
+    two norms around it.  ``names`` has the keys of :class:`PreNormBlock` plus ``mixer_post`` and
+    ``ffn_post``."""
+
+    def __init__(self, width: int, mixer: Mixer, feed_forward, mixer_norm: Norm, mixer_post: Norm, ffn_norm,
+                 ffn_post, names: Dict[str, str]):
+        super().__init__(width, mixer, feed_forward, mixer_norm, ffn_norm, names)
+        self.mixer_post, self.ffn_post = mixer_post, ffn_post
+
+    def _children(self, prefix: str):
+        kids = super()._children(prefix) + [(self.mixer_post, f"{prefix}.{self.names['mixer_post']}"),
+                                            (self.ffn_post, f"{prefix}.{self.names['ffn_post']}")]
+        return [(p, n) for p, n in kids if p is not None]
+
+    def forward(self, ctx: StepContext, x: torch.Tensor, cache) -> None:
+        xn = ctx.workspace.rows("normed", ctx.n, self.width, ctx.act_dtype)
+        out = ctx.workspace.rows("sublayer_out", ctx.n, self.width, torch.float32)
+        self.mixer_norm.forward(ctx, x, xn)
+        self.mixer.forward(ctx, xn, out, cache, accumulate=False)
+        self.mixer_post.forward_residual(ctx, out, x)
+        if self.feed_forward is None:
+            return
+        self.ffn_norm.forward(ctx, x, xn)
+        self.feed_forward.forward(ctx, xn, out, accumulate=False)
+        self.ffn_post.forward_residual(ctx, out, x)

@@ -19,10 +19,12 @@ class TokenEmbedding(Part):
     graph_safe = True  # kernels only: a step through this part can be captured
 
     def __init__(self, vocab: int, width: int, name: str = "embed_tokens", tensor: Optional[str] = None,
-                 norm: Optional[Norm] = None, norm_tensor: Optional[str] = None):
+                 norm: Optional[Norm] = None, norm_tensor: Optional[str] = None, scale: float = 1.0):
         """``tensor``: the table's full name where it is not ``<prefix>.<name>.weight``.  ``norm``:
-        a norm applied to the embedded rows in place on the stream, its weight named ``norm_tensor``."""
+        a norm applied to the embedded rows in place on the stream, its weight named ``norm_tensor``.
+        ``scale``: a constant that the embedded rows are multiplied by (in 32-bit)."""
         self.vocab, self.width, self.name = vocab, width, name
+        self.scale = float(scale)
         self.tensor, self.norm, self.norm_tensor = tensor, norm, norm_tensor
         self.table: Optional[torch.Tensor] = None
 
@@ -44,7 +46,10 @@ class TokenEmbedding(Part):
         return self.table.numel() * self.table.element_size() + (self.norm.param_bytes() if self.norm else 0)
 
     def forward(self, ctx: StepContext, x: torch.Tensor) -> None:
-        ctx.ops.embed_rows(self.table, ctx.tokens, x)
+        if self.scale != 1.0:
+            ctx.ops.embed_rows(self.table, ctx.tokens, x, scale=self.scale)
+        else:
+            ctx.ops.embed_rows(self.table, ctx.tokens, x)
         if self.norm is not None:
             self.norm.forward(ctx, x, x)
 
@@ -53,8 +58,10 @@ class OutputHead(Part):
     graph_safe = True  # kernels only: a step through this part can be captured
 
     def __init__(self, vocab: int, width: int, norm: Norm, tied_to: Optional[TokenEmbedding] = None,
-                 norm_name: str = "model.norm", head_name: str = "lm_head"):
+                 norm_name: str = "model.norm", head_name: str = "lm_head", suffix: str = ".weight"):
+        """A constant scale of the logits belongs to ``norm`` as its ``gain`` (the product is linear)."""
         self.vocab, self.width = vocab, width
+        self.suffix = suffix
         self.norm, self.tied_to = norm, tied_to
         self.norm_name, self.head_name = norm_name, head_name
         self.weight: Optional[torch.Tensor] = None
@@ -62,12 +69,12 @@ class OutputHead(Part):
     def param_specs(self, prefix: str = "") -> List[ParamSpec]:
         specs = self.norm.param_specs(self.norm_name)
         if self.tied_to is None:
-            specs.append(ParamSpec(f"{self.head_name}.weight", (self.vocab, self.width), MATRIX))
+            specs.append(ParamSpec(f"{self.head_name}{self.suffix}", (self.vocab, self.width), MATRIX))
         return specs
 
     def load_params(self, state: Dict[str, torch.Tensor], prefix: str = "") -> None:
         self.norm.load_params(state, self.norm_name)
-        self.weight = self.tied_to.table if self.tied_to is not None else state[f"{self.head_name}.weight"]
+        self.weight = self.tied_to.table if self.tied_to is not None else state[f"{self.head_name}{self.suffix}"]
 
     def param_bytes(self) -> int:
         own = 0 if self.tied_to is not None else self.weight.numel() * self.weight.element_size()

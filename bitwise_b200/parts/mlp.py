@@ -15,23 +15,27 @@ from .base import FeedForward, StepContext, register_feed_forward
 class SwiGLU(FeedForward):
     graph_safe = True  # kernels only: a step through this part can be captured
 
-    def __init__(self, width: int, intermediate: int, names=("gate_proj", "up_proj", "down_proj")):
+    def __init__(self, width: int, intermediate: int, names=("gate_proj", "up_proj", "down_proj"),
+                 suffix: str = ".weight"):
         self.width, self.intermediate = width, intermediate
         self.names = names
+        self.suffix = suffix  # what follows a matrix's name in the checkpoint
         self.w_gate_up: Optional[torch.Tensor] = None  # rows [gate | up], or interleaved when fused
         self.w_down: Optional[torch.Tensor] = None
         self.fused = False  # gate/up product and SwiGLU in one kernel
 
     def param_specs(self, prefix: str) -> List[ParamSpec]:
         g, u, d = self.names
-        return [ParamSpec(f"{prefix}.{g}.weight", (self.intermediate, self.width), MATRIX),
-                ParamSpec(f"{prefix}.{u}.weight", (self.intermediate, self.width), MATRIX),
-                ParamSpec(f"{prefix}.{d}.weight", (self.width, self.intermediate), MATRIX)]
+        sfx = self.suffix
+        return [ParamSpec(f"{prefix}.{g}{sfx}", (self.intermediate, self.width), MATRIX),
+                ParamSpec(f"{prefix}.{u}{sfx}", (self.intermediate, self.width), MATRIX),
+                ParamSpec(f"{prefix}.{d}{sfx}", (self.width, self.intermediate), MATRIX)]
 
     def load_params(self, state: Dict[str, torch.Tensor], prefix: str) -> None:
         g, u, d = self.names
-        self.w_gate_up = torch.cat([state[f"{prefix}.{g}.weight"], state[f"{prefix}.{u}.weight"]], 0).contiguous()
-        self.w_down = state[f"{prefix}.{d}.weight"]
+        sfx = self.suffix
+        self.w_gate_up = torch.cat([state[f"{prefix}.{g}{sfx}"], state[f"{prefix}.{u}{sfx}"]], 0).contiguous()
+        self.w_down = state[f"{prefix}.{d}{sfx}"]
 
     def param_bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in (self.w_gate_up, self.w_down))
@@ -44,7 +48,8 @@ class SwiGLU(FeedForward):
             self.w_gate_up = ops.interleave_gate_up(gate, up)
             self.fused = True
 
-    def forward(self, ctx: StepContext, xn: torch.Tensor, x: torch.Tensor) -> None:
+    def forward(self, ctx: StepContext, xn: torch.Tensor, x: torch.Tensor, accumulate: bool = True) -> None:
+        """``accumulate`` False: the output is written to ``x`` (float32) instead of added to it."""
         ops, n = ctx.ops, ctx.n
         h = ctx.workspace.rows("ffn_h", n, self.intermediate, ctx.act_dtype)
         if self.fused:
@@ -53,7 +58,7 @@ class SwiGLU(FeedForward):
             gate_up = ctx.workspace.rows("gate_up", n, 2 * self.intermediate, ctx.act_dtype)
             ops.linear(xn, self.w_gate_up, gate_up)
             ops.swiglu(gate_up, h)
-        ops.linear(h, self.w_down, x, residual=x)
+        ops.linear(h, self.w_down, x, residual=x if accumulate else None)
 
 
 register_feed_forward("swiglu", SwiGLU)

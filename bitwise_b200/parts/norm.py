@@ -2,7 +2,10 @@
 (src/kernels.cpp:264-271), and layer norm with a weight and no bias: y = (x - mean) / sqrt(var +
 eps) * w with var the mean of the squared deviations.  The statistics are always computed in
 32-bit.  ``suffix`` is what follows the prefix in the tensor's name (".weight" in Hugging Face
-checkpoints, nothing where the tensor carries the norm's own name)."""
+checkpoints, nothing where the tensor carries the norm's own name).  A norm may hold its weight
+around zero (``offset`` 1: the factor is 1 + w) and carry a constant ``gain`` (a model's output
+scale applied with its last norm); both are folded into the 32-bit weight once, when it is loaded:
+the kernels multiply by ``(offset + w) * gain``."""
 from __future__ import annotations
 
 from typing import Dict, List, Optional
@@ -16,23 +19,33 @@ from .base import Norm, StepContext, register_norm
 class RMSNorm(Norm):
     graph_safe = True  # kernels only: a step through this part can be captured
 
-    def __init__(self, width: int, eps: float, suffix: str = ".weight"):
+    def __init__(self, width: int, eps: float, suffix: str = ".weight", offset: float = 0.0, gain: float = 1.0):
         self.width = width
         self.eps = float(eps)
         self.suffix = suffix
+        self.offset, self.gain = float(offset), float(gain)
         self.weight: Optional[torch.Tensor] = None
 
     def param_specs(self, prefix: str) -> List[ParamSpec]:
-        return [ParamSpec(prefix + self.suffix, (self.width,), KEEP32, init="ones")]
+        return [ParamSpec(prefix + self.suffix, (self.width,), KEEP32, init="zeros" if self.offset else "ones")]
 
     def load_params(self, state: Dict[str, torch.Tensor], prefix: str) -> None:
-        self.weight = state[prefix + self.suffix]
+        w = state[prefix + self.suffix]
+        if self.offset:
+            w = w + self.offset
+        if self.gain != 1.0:
+            w = w * self.gain
+        self.weight = w
 
     def param_bytes(self) -> int:
         return self.weight.numel() * self.weight.element_size()
 
     def forward(self, ctx: StepContext, x, out, rows=None) -> None:
         ctx.ops.rmsnorm(x, self.weight, self.eps, out, rows)
+
+    def forward_residual(self, ctx: StepContext, d, x) -> None:
+        """x += norm(d): the norm of a sublayer's output ``d`` (float32) on its way into the stream."""
+        ctx.ops.rmsnorm_residual(d, self.weight, self.eps, x)
 
 
 class LayerNorm(RMSNorm):

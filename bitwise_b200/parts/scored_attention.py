@@ -1,0 +1,160 @@
+"""Grouped-query softmax attention over paged keys and values, with its steps as options.
+
+Before the scores, each on or off by a constructor argument:
+
+* a short causal convolution over time on every channel of q, k and v, directly after the
+  projection: ``y_t = sum_j w[:, j] * u_(t - taps + 1 + j)``, zeros before the sequence's start.
+  The last ``taps - 1`` projected rows of a request are its state, kept in a state slot;
+* a root-mean-square norm of every head of q and of k, with one weight of the head's size each;
+* a rotation of the first ``rot_dims`` entries of every head of q and k: entries 2i and 2i + 1
+  form pair i, turned by ``pos * base ** (-2i / rot_dims)`` (tables from a ``RotaryEncoding``).
+
+On the scores ``s = (q . k) * scale``:
+
+* ``softcap``: ``s <- cap * tanh(s / cap)``;
+* ``slopes``: ``s <- s - slope_h * (i - j)`` for query position i and key position j;
+* ``window``: position i sees the keys j with ``0 <= i - j < window`` (every j <= i without);
+* ``sink``: one is added to the softmax's denominator (a key of score 0 that has no value).
+
+``values_are_keys``: there is no value projection and nothing but the keys is cached; the
+weighted sum runs over the keys as projected.  ``shares_cache``: the layer has no key and value
+tensors; it reads the pages that an earlier layer wrote (keys after convolution, norm and
+rotation; values after convolution), with its own queries and its own convolution state.
+
+Projections may run in the activation type; what follows them up to the stored key (convolution,
+norm, rotation), the scores and the softmax weights are 32-bit in both precisions.  Head h reads
+key/value head ``h // (heads / kv_heads)``.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from ..weights.loader import KEEP32, MATRIX, ParamSpec
+from .base import Mixer, PagedKVNeed, PagedKVView, PositionEncoding, SlotStateNeed, StepContext, register_mixer
+
+
+def distance_slopes(heads: int, exponent: float = 8.0) -> List[float]:
+    """slope_h = 2 ** (-exponent * (h + 1) / heads) for h = 0 .. heads - 1."""
+    return [2.0 ** (-exponent * (h + 1) / heads) for h in range(heads)]
+
+
+class ScoredAttention(Mixer):
+    graph_safe = True  # kernels only; launches depend on the step's sizes and ctx.max_keys
+
+    NAMES = {"q": "q", "k": "k", "v": "v", "out": "o", "conv": ".conv", "norm": ".norm"}
+
+    def __init__(self, width: int, heads: int, kv_heads: int, dim: int, vdim: int, scale: float, eps: float = 1e-6,
+                 conv_taps: int = 0, qk_norm: bool = False, position: Optional[PositionEncoding] = None, rot_dims: int = 0,
+                 softcap: Optional[float] = None, sink: bool = False, slopes: Optional[Sequence[float]] = None,
+                 window: Optional[int] = None, values_are_keys: bool = False, shares_cache: bool = False,
+                 names: Optional[Dict[str, str]] = None):
+        if heads % kv_heads:
+            raise ValueError(f"{heads} heads are not a multiple of {kv_heads} key/value heads")
+        if values_are_keys and vdim != dim:
+            raise ValueError("values that are the keys have the keys' size")
+        if slopes is not None and len(slopes) != heads:
+            raise ValueError("one slope per head is needed")
+        if rot_dims % 2 or rot_dims > dim:
+            raise ValueError(f"{rot_dims} turned entries do not fit a head of {dim}")
+        self.width, self.heads, self.kv_heads, self.dim, self.vdim = width, heads, kv_heads, dim, vdim
+        self.scale, self.eps = float(scale), float(eps)
+        self.taps = int(conv_taps or 0)  # 0: no convolution; 1: a factor per channel and no state
+        self.qk_norm, self.position, self.rot_dims = qk_norm, position, rot_dims
+        self.softcap, self.sink, self.window = softcap, bool(sink), window
+        self.slopes_host = [float(s) for s in slopes] if slopes is not None else None
+        self.values_are_keys, self.shares_cache = values_are_keys, shares_cache
+        self.names = dict(self.NAMES, **(names or {}))
+        self.q_cols = heads * dim
+        self.k_cols = 0 if shares_cache else kv_heads * dim
+        self.v_cols = 0 if shares_cache or values_are_keys else kv_heads * vdim
+        self.cols = self.q_cols + self.k_cols + self.v_cols
+        self.w_in = self.w_o = self.conv_w = self.q_norm = self.k_norm = self.slopes = None
+
+    # -- what the cache keeps --------------------------------------------------------------
+    def cache_need(self):
+        return PagedKVNeed(self.kv_heads, self.dim, self.window, v_dim=0 if self.values_are_keys else self.vdim)
+
+    def state_need(self):
+        """The convolution's inputs of the last ``taps - 1`` positions, for every channel it runs on."""
+        if self.taps <= 1:
+            return None
+        return SlotStateNeed((self.taps - 1, self.cols), torch.float32)
+
+    def query_tile_rows(self, ops=None):
+        group = self.heads // self.kv_heads
+        heights = list(ops.scored_attention_tile_heights(group, self.dim, self.vdim)) if ops is not None and hasattr(
+            ops, "scored_attention_tile_heights") else [max(1, 32 // group)]
+        if self.taps > 1:
+            heights.append(SEQUENCE_TILE)
+        return heights
+
+    # -- parameters ------------------------------------------------------------------------
+    def _projections(self):
+        n = self.names
+        out = [(n["q"], self.q_cols, self.dim, True)]
+        if not self.shares_cache:
+            out.append((n["k"], self.k_cols, self.dim, True))
+            if not self.values_are_keys:
+                out.append((n["v"], self.v_cols, self.vdim, False))
+        return out  # (name, columns, head size, normed)
+
+    def param_specs(self, prefix: str) -> List[ParamSpec]:
+        n = self.names
+        specs = []
+        for name, cols, size, normed in self._projections():
+            specs.append(ParamSpec(f"{prefix}.{name}", (cols, self.width), MATRIX))
+            if self.taps:
+                specs.append(ParamSpec(f"{prefix}.{name}{n['conv']}", (cols, self.taps), KEEP32))
+            if self.qk_norm and normed:
+                specs.append(ParamSpec(f"{prefix}.{name}{n['norm']}", (size,), KEEP32, init="ones"))
+        specs.append(ParamSpec(f"{prefix}.{n['out']}", (self.width, self.heads * self.vdim), MATRIX))
+        return specs
+
+    def load_params(self, state: Dict[str, torch.Tensor], prefix: str) -> None:
+        n = self.names
+        proj = self._projections()
+        ws = [state[f"{prefix}.{name}"] for name, _, _, _ in proj]
+        self.w_in = torch.cat(ws, 0).contiguous() if len(ws) > 1 else ws[0]
+        if self.taps:
+            self.conv_w = torch.cat([state[f"{prefix}.{name}{n['conv']}"] for name, _, _, _ in proj], 0).contiguous()
+        if self.qk_norm:
+            self.q_norm = state[f"{prefix}.{n['q']}{n['norm']}"]
+            self.k_norm = None if self.shares_cache else state[f"{prefix}.{n['k']}{n['norm']}"]
+        self.w_o = state[f"{prefix}.{n['out']}"]
+        if self.slopes_host is not None:
+            self.slopes = torch.tensor(self.slopes_host, dtype=torch.float32, device=self.w_o.device)
+
+    def param_bytes(self) -> int:
+        ts = (self.w_in, self.w_o, self.conv_w, self.q_norm, self.k_norm)
+        return sum(t.numel() * t.element_size() for t in ts if t is not None)
+
+    # -- one step --------------------------------------------------------------------------
+    def forward(self, ctx: StepContext, xn: torch.Tensor, x: torch.Tensor, cache: PagedKVView,
+                accumulate: bool = True) -> None:
+        """``accumulate`` False: the output is written to ``x`` instead of added to it."""
+        ops, ws, n = ctx.ops, ctx.workspace, ctx.n
+        u = ws.rows("scored_qkv32", n, self.cols, torch.float32)
+        ops.linear(xn, self.w_in, u)
+        tables = self.position.rotary_tables(x.device) if self.position is not None and self.rot_dims else None
+        cos, sin = tables if tables is not None else (None, None)
+        q = ws.rows("scored_q", n, self.q_cols, ctx.act_dtype)
+        state = cache.state if self.taps > 1 else None
+        writes = cache.writable and not self.shares_cache
+        ops.qkv_prepare(u, self.conv_w, state.state if state is not None else None, self.q_norm, self.k_norm, self.eps,
+                        cos, sin, ctx, cache.block_table, cache.k, cache.v, q, self.heads,
+                        self.kv_heads if writes else 0, self.dim, self.vdim)
+        if state is not None:
+            ops.conv_state_update(u, state.state, ctx, self.taps, ctx.query_tiles(SEQUENCE_TILE))
+        mixed = ws.rows("scored_mixed", n, self.heads * self.vdim, ctx.act_dtype)
+        ops.scored_attention(q, cache.k, cache.v, cache.block_table, mixed, self.heads, self.kv_heads, self.dim, self.vdim,
+                             self.scale, self.softcap or 0.0, self.sink, self.slopes, self.window or 0, ctx)
+        ops.linear(mixed, self.w_o, x, residual=x if accumulate else None)
+
+
+# A query-tile height larger than any step: the step's tile list of this height has one entry
+# per sequence (sequence, first row, rows), which is what kernels that walk a sequence need.
+SEQUENCE_TILE = 1 << 20
+
+register_mixer("scored_attention", ScoredAttention)

@@ -83,8 +83,8 @@ def random_tensors(specs: Iterable[ParamSpec], seed: int, dtype: torch.dtype = t
         numel = int(np.prod(s.shape)) if s.shape else 1
         if s.kind == INT_TABLE:
             raise ValueError(f"no random rule for the integer table {s.name}")
-        if s.init == "ones":
-            v = np.ones(numel, dtype=np.float64)
+        if s.init in ("ones", "zeros"):  # a norm's weight: around one, or around zero where the norm adds one
+            v = np.full(numel, 1.0 if s.init == "ones" else 0.0, dtype=np.float64)
             if norm_jitter:
                 v = v + uniform_values(seed, s.name, numel, -norm_jitter, norm_jitter)
         else:

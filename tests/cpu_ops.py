@@ -20,8 +20,117 @@ class CpuOps:
         self.kind = "f32" if dtype == "float32" else "bf16"
         self.launches = 0
 
-    def embed_rows(self, table, tokens, out):
-        out.copy_(table[tokens.long()].float())
+    def embed_rows(self, table, tokens, out, scale=1.0):
+        out.copy_(table[tokens.long()].float() * scale)
+
+    def rmsnorm_residual(self, d, weight, eps, x):
+        x += (d * torch.rsqrt(d.pow(2).mean(-1, keepdim=True) + eps)) * weight
+
+    # -- scored attention and the linear recurrence (stand-ins shaped like the kernels' interface) --
+    def scored_attention_tile_heights(self, group, dim, vdim):
+        return [max(1, 32 // group)]
+
+    def qkv_prepare(self, u, conv_w, conv_state, q_norm, k_norm, eps, cos, sin, ctx, block_table, kcache, vcache, q_out,
+                    heads, write_kv_heads, dim, vdim):
+        n, cols = u.shape
+        page = kcache.shape[2]
+        y = u.clone()
+        if conv_w is not None:
+            taps = conv_w.shape[1]
+            y.zero_()
+            for r in range(n):
+                s = int(ctx.row_seq[r])
+                row0, pos0, slot = int(ctx.seq_row0[s]), int(ctx.seq_pos0[s]), int(ctx.seq_slot[s])
+                for j in range(taps):
+                    back = taps - 1 - j
+                    if int(ctx.pos[r]) - back < 0:
+                        continue
+                    src = u[r - back] if r - back >= row0 else conv_state[slot, taps - 1 - (row0 - (r - back))]
+                    y[r] += conv_w[:, j] * src
+        p = ctx.pos.long()
+
+        def finish(t, size, w):
+            t = t.reshape(n, -1, size)
+            if w is not None:
+                t = t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + eps) * w
+            if cos is not None:
+                pairs = cos.shape[1]
+                c, sn = cos[p][:, None, :], sin[p][:, None, :]
+                a, b = t[..., 0:2 * pairs:2].clone(), t[..., 1:2 * pairs:2].clone()
+                t = t.clone()
+                t[..., 0:2 * pairs:2] = a * c - b * sn
+                t[..., 1:2 * pairs:2] = b * c + a * sn
+            return t
+
+        q_out.copy_(finish(y[:, :heads * dim], dim, q_norm).reshape(n, -1).to(q_out.dtype))
+        if not write_kv_heads:
+            return
+        g = write_kv_heads
+        k = finish(y[:, heads * dim:(heads + g) * dim], dim, k_norm)
+        v = y[:, (heads + g) * dim:].reshape(n, g, vdim) if vcache is not None else None
+        for r in range(n):
+            blk = int(block_table[int(ctx.row_seq[r]), int(p[r]) // page])
+            kcache[blk, :, int(p[r]) % page, :] = k[r].to(kcache.dtype)
+            if v is not None:
+                vcache[blk, :, int(p[r]) % page, :] = v[r].to(vcache.dtype)
+
+    def conv_state_update(self, u, state, ctx, taps, tiles):
+        t_seq, t_row0, t_rows, count = tiles
+        for i in range(count):
+            s, row0, cnt = int(t_seq[i]), int(t_row0[i]), int(t_rows[i])
+            slot, pos0 = int(ctx.seq_slot[s]), int(ctx.seq_pos0[s])
+            old = state[slot].clone()
+            for j in range(taps - 1):
+                pos = pos0 + cnt - (taps - 1) + j
+                if pos < 0:
+                    state[slot, j] = 0
+                elif pos >= pos0:
+                    state[slot, j] = u[row0 + pos - pos0]
+                else:
+                    state[slot, j] = old[pos - pos0 + taps - 1]
+
+    def scored_attention(self, q, kcache, vcache, block_table, out, heads, kv_heads, dim, vdim, scale, softcap, sink,
+                         slopes, window, ctx):
+        n = q.shape[0]
+        page = kcache.shape[2]
+        grp = heads // kv_heads
+        for r in range(n):
+            p = int(ctx.pos[r])
+            lo = max(0, p - window + 1) if window else 0
+            idx = torch.arange(lo, p + 1)
+            blocks = block_table[int(ctx.row_seq[r])][(idx // page).long()].long()
+            slots = (idx % page).long()
+            k = kcache[blocks, :, slots, :].float().repeat_interleave(grp, dim=1)
+            v = k if vcache is None else vcache[blocks, :, slots, :].float().repeat_interleave(grp, dim=1)
+            s = torch.einsum("hd,khd->hk", q[r].float().view(heads, dim), k) * scale
+            if softcap:
+                s = softcap * torch.tanh(s / softcap)
+            if slopes is not None:
+                s = s - slopes[:, None] * (p - idx).float()[None, :]
+            m = s.max(-1, keepdim=True).values
+            e = torch.exp(s - m)
+            den = e.sum(-1, keepdim=True) + (torch.exp(-m) if sink else 0.0)
+            out[r] = torch.einsum("hk,khd->hd", e / den, v).reshape(-1).to(out.dtype)
+
+    def gla_scan(self, u, z, bias, tau, state, norm_w, eps, out, heads, dim, vdim, q_scale, ctx, tiles):
+        t_seq, t_row0, t_rows, count = tiles
+        hd, hv = heads * dim, heads * vdim
+        for i in range(count):
+            s, row0, cnt = int(t_seq[i]), int(t_row0[i]), int(t_rows[i])
+            slot = int(ctx.seq_slot[s])
+            S = state[slot]
+            if int(ctx.seq_pos0[s]) == 0:
+                S.zero_()
+            for r in range(row0, row0 + cnt):
+                qv = u[r, :hd].view(heads, dim) * q_scale
+                kv = u[r, hd:2 * hd].view(heads, dim)
+                vv = u[r, 2 * hd:2 * hd + hv].view(heads, vdim)
+                gate = u[r, 2 * hd + hv:]
+                decay = torch.exp(torch.nn.functional.logsigmoid(z[r] + bias) / tau).view(heads, dim)
+                S.mul_(decay[:, :, None]).add_(kv[:, :, None] * vv[:, None, :])
+                o = torch.einsum("hd,hde->he", qv, S)
+                o = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + eps) * norm_w
+                out[r] = (o.reshape(-1) * gate * torch.sigmoid(gate)).to(out.dtype)
 
     def rmsnorm(self, x, weight, eps, out, rows=None):
         src = x if rows is None else x[rows.long()]
