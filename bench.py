@@ -508,6 +508,167 @@ def compare_nuderax(args, pk):
     return line
 
 
+# ---- the Favudra design beside Llama at equal size (--compare favudra) -------------------------
+FAVUDRA_SIZES = {
+    # width, layers, heads, kv_heads, dim = vdim, ff, window, taps, recurrence heads x (dim, vdim), decay rank, vocab
+    "small": dict(width=1024, layers=4, heads=8, kv_heads=2, dim=128, ff=2816, window=512, taps=4, rot_dims=64,
+                  gla_heads=8, gla_dim=64, gla_vdim=128, decay_rank=32, vocab=32768),
+    "medium": dict(width=2048, layers=4, heads=16, kv_heads=4, dim=128, ff=5632, window=1024, taps=4, rot_dims=64,
+                   gla_heads=16, gla_dim=128, gla_vdim=128, decay_rank=64, vocab=32768),
+}
+
+
+def favudra_config(z):
+    """Layers in the order recurrence, attention, window attention, attention on the second layer's
+    keys and values, and so on; every layer with a feed-forward."""
+    from bitwise_b200.config import FavudraConfig, FavudraLayerConfig, FavudraMixerConfig
+    layers = []
+    for i in range(z["layers"]):
+        kind = i % 4
+        if kind == 0:
+            m = FavudraMixerConfig("gla", z["gla_heads"], z["gla_dim"], z["gla_vdim"], tau=16.0, decay_rank=z["decay_rank"])
+        elif kind == 2:
+            m = FavudraMixerConfig("attention_2", z["heads"], z["dim"], z["dim"], kv_heads=z["kv_heads"],
+                                   scale=z["dim"] ** -0.5, window=z["window"])
+        else:
+            m = FavudraMixerConfig("attention", z["heads"], z["dim"], z["dim"], kv_heads=z["kv_heads"], scale=z["dim"] ** -0.5,
+                                   conv=z["taps"], rot_base=1e6, rot_dims=z["rot_dims"], softcap=30.0,
+                                   kv_from=i - 2 if kind == 3 else None)
+        layers.append(FavudraLayerConfig(m, z["ff"]))
+    return FavudraConfig(vocab=z["vocab"], width=z["width"], eps=1e-5, embedding_scale=z["width"] ** 0.5, logit_scale=0.25,
+                         layers=tuple(layers))
+
+
+def favudra_twin(z):
+    """Llama with the same width, layers, heads, key/value heads, head size, feed-forward and vocabulary."""
+    from bitwise_b200 import LlamaConfig
+    return LlamaConfig(vocab_size=z["vocab"], hidden_size=z["width"], num_hidden_layers=z["layers"],
+                       num_attention_heads=z["heads"], num_key_value_heads=z["kv_heads"], head_dim=z["dim"],
+                       intermediate_size=z["ff"], rope_theta=1e6, rms_norm_eps=1e-5, tie_word_embeddings=False,
+                       max_position_embeddings=8192)
+
+
+def favudra_kernel_table(z, pk, page=16):
+    """Every new kernel alone at the size's shapes beside the like kernel of the Llama twin:
+    milliseconds and the fraction of its roofline (measured copy bandwidth or bf16 peak)."""
+    import torch
+    from bitwise_b200.kernels.ops import get_ops
+    from bitwise_b200.parts.rope import RotaryEncoding
+    from bitwise_b200.parts.scored_attention import SEQUENCE_TILE, distance_slopes
+    ops = get_ops("bfloat16")
+    dev, bf = "cuda:0", torch.bfloat16
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    H, G, hd, width, win, taps = z["heads"], z["kv_heads"], z["dim"], z["width"], z["window"], z["taps"]
+    gh, gd, gv = z["gla_heads"], z["gla_dim"], z["gla_vdim"]
+    out = {}
+
+    def frac_flops(flops, ms):
+        return round(flops / (ms / 1e3) / 1e12 / pk["bf16_tflops"], 4)
+
+    def frac_bytes(nbytes, ms):
+        return round(nbytes / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 4)
+
+    def put(name, ms, frac, twin_ms, twin_frac, bound):
+        out[name] = {"ms": round(ms, 4), "frac": frac, "twin_ms": round(twin_ms, 4), "twin_frac": twin_frac, "bound": bound,
+                     "gap_ratio": round(twin_frac / frac, 2) if frac else None}
+
+    cos, sin = RotaryEncoding(z["rot_dims"], 1e6, positions=2048).rotary_tables(dev)
+    cos_t, sin_t = RotaryEncoding(hd, 1e6, positions=2048).rotary_tables(dev)
+    slopes = torch.tensor(distance_slopes(H), dtype=torch.float32, device=dev)
+    for label, seqs in (("prefill_2048", [(0, 2048)]), ("decode_b8_ctx2048", [(2047, 1)] * 8)):
+        keys = max(p0 + c for p0, c in seqs)
+        blocks = (keys + page - 1) // page
+        nseq = len(seqs)
+        table = torch.arange(nseq * blocks, dtype=torch.int32, device=dev).reshape(nseq, blocks)
+        heights = set(ops.scored_attention_tile_heights(H // G, hd, hd)) | set(ops.attention_tile_heights(H, G, hd)) | {SEQUENCE_TILE}
+        b = KernelBatch(seqs, sorted(heights), dev)
+        b.seq_slot = torch.arange(nseq, dtype=torch.int32, device=dev)
+        n = b.n
+        prefill = n > nseq
+        pairs = sum(c * p0 + c * (c + 1) // 2 for p0, c in seqs)
+        wpairs = sum(sum(min(p + 1, win) for p in range(p0, p0 + c)) for p0, c in seqs)
+        kc = torch.randn(nseq * blocks + 1, G, page, hd, device=dev).to(bf)
+        vc = torch.randn(nseq * blocks + 1, G, page, hd, device=dev).to(bf)
+        q = torch.randn(n, H * hd, device=dev).to(bf)
+        o = torch.empty(n, H * hd, dtype=bf, device=dev)
+        qkv = torch.randn(n, (H + 2 * G) * hd, device=dev).to(bf)
+        twin = lambda w: timed(lambda: ops.attention(qkv, kc, vc, table, b.row_seq, b.pos, o, H, G, hd, w, b.max_keys,
+                                                     hd ** -0.5, batch=b), flush=flush)
+        ms = timed(lambda: ops.scored_attention(q, kc, vc, table, o, H, G, hd, hd, hd ** -0.5, 30.0, True, None, 0, b), flush=flush)
+        tms = twin(0)
+        ms2 = timed(lambda: ops.scored_attention(q, kc, None, table, o, H, G, hd, hd, hd ** -0.5, 0.0, False, slopes, win, b),
+                    flush=flush)
+        tms2 = twin(win)
+        if prefill:
+            put(f"attention_{label}", ms, frac_flops(4.0 * H * hd * pairs, ms), tms, frac_flops(4.0 * H * hd * pairs, tms), "bf16 peak")
+            put(f"window_attention_{label}", ms2, frac_flops(4.0 * H * hd * wpairs, ms2), tms2,
+                frac_flops(4.0 * H * hd * wpairs, tms2), "bf16 peak")
+        else:
+            put(f"attention_{label}", ms, frac_bytes(nseq * keys * 2 * G * hd * 2, ms), tms,
+                frac_bytes(nseq * keys * 2 * G * hd * 2, tms), "copy bandwidth")
+            put(f"window_attention_{label}", ms2, frac_bytes(nseq * min(keys, win) * G * hd * 2, ms2), tms2,
+                frac_bytes(nseq * min(keys, win) * 2 * G * hd * 2, tms2), "copy bandwidth")
+        # convolution, norm, rotation and the way into the pages, beside the twin's rotation and store
+        cols = (H + 2 * G) * hd
+        u = torch.randn(n, cols, device=dev)
+        cw = torch.randn(cols, taps, device=dev)
+        st = torch.zeros(nseq + 1, taps - 1, cols, device=dev)
+        nw = torch.ones(hd, device=dev)
+        ms = timed(lambda: (ops.qkv_prepare(u, cw, st, nw, nw, 1e-5, cos, sin, b, table, kc, vc, q, H, G, hd, hd),
+                            ops.conv_state_update(u, st, b, taps, b.query_tiles(SEQUENCE_TILE))), flush=flush)
+        tms = timed(lambda: ops.rope_cache(qkv, b.pos, b.row_seq, cos_t, sin_t, table, kc, vc, H, G, hd), flush=flush)
+        put(f"conv_norm_rotate_store_{label}", ms, frac_bytes(n * cols * 6, ms), tms, frac_bytes(n * cols * 4, tms), "copy bandwidth")
+        # the norm after a sublayer beside the twin's norm
+        d = torch.randn(n, width, device=dev)
+        stream = torch.randn(n, width, device=dev)
+        wn = torch.ones(width, device=dev)
+        a1 = torch.empty(n, width, dtype=bf, device=dev)
+        ms = timed(lambda: ops.rmsnorm_residual(d, wn, 1e-5, stream), flush=flush)
+        tms = timed(lambda: ops.rmsnorm(stream, wn, 1e-5, a1), flush=flush)
+        put(f"norm_after_sublayer_{label}", ms, frac_bytes(n * width * 12, ms), tms, frac_bytes(n * width * 6, tms), "copy bandwidth")
+        # the recurrence: no like kernel in the twin; per token and head 4 dim vdim operations on the
+        # CUDA cores, and in a decode step the state read and written once
+        uu = torch.randn(n, 2 * gh * (gd + gv), device=dev)
+        zz = torch.randn(n, gh * gd, device=dev)
+        state = torch.zeros(nseq + 1, gh, gd, gv, device=dev)
+        og = torch.empty(n, gh * gv, dtype=bf, device=dev)
+        ms = timed(lambda: ops.gla_scan(uu, zz, torch.zeros(gh * gd, device=dev), 16.0, state, torch.ones(gv, device=dev), 1e-5,
+                                        og, gh, gd, gv, gd ** -0.5, b, b.query_tiles(SEQUENCE_TILE)), flush=flush)
+        if prefill:
+            out[f"recurrence_{label}"] = {"ms": round(ms, 4), "frac": round(4.0 * n * gh * gd * gv / (ms / 1e3) / 1e12 /
+                                                                             pk.get("fp32_tflops", 74.0), 4),
+                                          "bound": "float32 on the CUDA cores; a sequence's tokens are walked one after the other"}
+        else:
+            out[f"recurrence_{label}"] = {"ms": round(ms, 4), "frac": frac_bytes(nseq * gh * gd * gv * 8, ms), "bound": "copy bandwidth"}
+        del kc, vc
+        torch.cuda.empty_cache()
+    return out
+
+
+def compare_favudra(args, pk):
+    import torch
+    from bitwise_b200 import Model
+    z = FAVUDRA_SIZES[args.size]
+    line = {"metric": f"Favudra beside Llama at equal size ({args.size}): prefill of 2,048 tokens and decode at batch "
+                      f"{args.batch}, {args.ctx or 2048:,}-token contexts", "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16",
+            "data": "synthetic: random N(0,0.02) weights, prompt ids uniform over the vocabulary", "size": z,
+            "peaks": "of " + pk["source"], "l2": "whole models: weights and cache exceed L2; kernels alone: L2 flushed "
+            "before every repetition"}
+    ctx = args.ctx or 2048
+    for name, cfg in (("favudra", favudra_config(z)), ("llama_twin", favudra_twin(z))):
+        model = Model.random(cfg, seed=0, dtype="bfloat16", device="cuda:0", fast=True)
+        with ClockSampler() as clocks:
+            ms, launches = run_decode(model, args.batch, ctx, args.steps, max(3, args.warmup), args.page)
+        pms = run_prefill(model, 2048, reps=5, warmup=3, page=args.page)
+        line[name] = {"decode_tok_s": round(args.batch / (ms / 1e3), 1), "decode_ms_per_step": round(ms, 4),
+                      "prefill_tok_s": round(2048 / (pms / 1e3), 1), "prefill_ms": round(pms, 3),
+                      "weight_bytes": model.weight_bytes, "gpu_launches": launches, "clocks": clocks.summary()}
+        del model
+        torch.cuda.empty_cache()
+    line["kernels"] = favudra_kernel_table(z, pk, args.page)
+    return line
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -526,9 +687,10 @@ def main():
     ap.add_argument("--page", type=int, default=16)
     ap.add_argument("--skip-points", action="store_true", help="only the headline decode (for profiling runs)")
     ap.add_argument("--skip-prefill", action="store_true")
-    ap.add_argument("--compare", default="", choices=["", "nuderax"],
+    ap.add_argument("--compare", default="", choices=["", "nuderax", "favudra"],
                     help="instead of the headline: this design beside the Llama architecture at equal size")
-    ap.add_argument("--size", default="small", choices=sorted(NUDERAX_SIZES), help="layer sizes for --compare")
+    ap.add_argument("--size", default="small", choices=sorted(set(NUDERAX_SIZES) | set(FAVUDRA_SIZES)),
+                    help="layer sizes for --compare")
     args = ap.parse_args()
 
     if args.gpus != 1:
@@ -544,6 +706,9 @@ def main():
     pk = peaks()
     if args.compare == "nuderax":
         print(json.dumps(compare_nuderax(args, pk)))
+        return 0
+    if args.compare == "favudra":
+        print(json.dumps(compare_favudra(args, pk)))
         return 0
     title, full_layers, _, shape_ctx = SHAPES[args.shape]
     args.layers = args.layers or full_layers
