@@ -61,7 +61,7 @@ __global__ void __launch_bounds__(kPrepWarps * 32) qkv_prepare_kernel(const Prep
   const int row0 = a.seq_row0[seq];
   const int slot = a.conv_state ? a.seq_slot[seq] : 0;
   const int total = a.heads + a.kv_heads + a.v_heads;
-  for (int hs = warp; hs < total; hs += kPrepWarps) {
+  for (int hs = blockIdx.y * kPrepWarps + warp; hs < total; hs += kPrepWarps * gridDim.y) {
     int size, col0;
     const float* norm_w;
     bool turns;
@@ -318,6 +318,290 @@ int launch_scored(dim3 grid, size_t smem, cudaStream_t stream, const act_t* q, i
   return bw::launch_status();
 }
 
+
+#if BW_ACT_BF16
+// ---------------------------------------------------------------------------------------
+// Attention on the tensor cores (bfloat16 operands, float32 accumulators; mma.sync m16n8k16).
+// A block of four warps takes 64 stacked queries (rows of one query tile x the query heads of one
+// key/value head), 16 per warp, and walks the keys in tiles of 32 at fixed absolute positions.
+// Scores stay in the accumulators as float32: scale, cap, distance slope, mask, the running
+// maximum and the weights exp(s - m) are formed there. The weights enter the second product as
+// two bfloat16 parts (p = hi + lo), so the values are weighted with 16 bits of p. A query's
+// result depends on its own keys and the fixed tiles only.
+constexpr int kMmaWarps = 4;
+constexpr int kMmaRows = 16 * kMmaWarps;
+constexpr int kMmaKeys = 32;
+
+template <int VD16 /* value size / 16 */>
+__global__ void __launch_bounds__(kMmaWarps * 32)
+scored_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv_bfloat16* __restrict__ kcache,
+                            const __nv_bfloat16* __restrict__ vcache, const int* __restrict__ block_table, int max_blocks,
+                            const int* __restrict__ tile_seq, const int* __restrict__ tile_row0,
+                            const int* __restrict__ tile_rows, const int* __restrict__ seq_pos0,
+                            const int* __restrict__ seq_row0, __nv_bfloat16* out, int o_stride, int heads, int kv_heads,
+                            int hb, int dim, int page, const ScoreArgs sa, int span_tiles, int spans, float* partial) {
+  bw::pdl_enter();
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  constexpr int vdim = VD16 * 16;
+  constexpr int VT = VD16 * 2;  // accumulator tiles of 8 value columns
+  const int kst = dim + 8;      // row strides in elements: 16 bytes more than a row, so that
+  const int vst_own = vdim + 8; // ldmatrix reads eight rows from eight different banks
+  __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [64][kst]
+  __nv_bfloat16* ks_all = qs + kMmaRows * kst;                      // [2][32][kst]: the tile in use and the next
+  __nv_bfloat16* vs_all = vcache ? ks_all + 2 * kMmaKeys * kst : ks_all;  // [2][32][vst]; the keys where values are keys
+  const int vst = vcache ? vst_own : kst;
+  const int t = blockIdx.x, g = blockIdx.y;
+  const int rep = heads / kv_heads;
+  const int zh = blockIdx.z / spans, span = blockIdx.z - zh * spans;  // the block's share of heads and of keys
+  const int h0 = g * rep + zh * hb;
+  const int nh = min(hb, rep - zh * hb);
+  const int seq = tile_seq[t], row0 = tile_row0[t], rows = tile_rows[t];
+  const int nq = rows * nh;
+  const int p0 = seq_pos0[seq] + (row0 - seq_row0[seq]);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int dparts = dim >> 3, vparts = vdim >> 3;
+  for (int c = tid; c < kMmaRows * dparts; c += kMmaWarps * 32) {
+    const int sr = c / dparts, part = c - sr * dparts;
+    const bool valid = sr < nq;
+    const __nv_bfloat16* src = valid ? q + static_cast<size_t>(row0 + sr / nh) * q_stride + (h0 + sr % nh) * dim + part * 8 : q;
+    bw::copy16_async(bw::smem_addr(qs + sr * kst + part * 8), src, valid);
+  }
+  bw::copies_commit();
+  // this thread's two queries: stacked rows sa_ and sb_ of the block
+  const int sr_a = warp * 16 + (lane >> 2), sr_b = sr_a + 8;
+  const bool ok_a = sr_a < nq, ok_b = sr_b < nq;
+  const int pq_a = p0 + (ok_a ? sr_a / nh : 0), pq_b = p0 + (ok_b ? sr_b / nh : 0);
+  const int lo_a = sa.window > 0 ? max(0, pq_a - sa.window + 1) : 0, lo_b = sa.window > 0 ? max(0, pq_b - sa.window + 1) : 0;
+  const float slope_a = sa.slopes && ok_a ? sa.slopes[h0 + sr_a % nh] : 0.0f;
+  const float slope_b = sa.slopes && ok_b ? sa.slopes[h0 + sr_b % nh] : 0.0f;
+  // the positions that this warp's queries span: tiles outside are skipped by the whole warp
+  const int w_first = min(warp * 16, max(nq - 1, 0)) / nh, w_last = min(warp * 16 + 15, max(nq - 1, 0)) / nh;
+  const int w_lo = sa.window > 0 ? max(0, p0 + w_first - sa.window + 1) : 0, w_hi = p0 + w_last;
+  const bool warp_has_rows = warp * 16 < nq;
+  float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.0f, l_b = 0.0f;
+  float acc[VT][4];
+#pragma unroll
+  for (int j = 0; j < VT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.0f;
+  const int last = p0 + rows - 1;
+  const int first = sa.window > 0 ? max(0, p0 - sa.window + 1) : 0;  // pages before it may be gone
+  const int* bt = block_table + static_cast<size_t>(seq) * max_blocks;
+  // With spans the block walks the key tiles span * span_tiles .. + span_tiles - 1 only (fixed
+  // absolute positions again) and leaves a record for the merge instead of the result.
+  int k_begin = first / kMmaKeys * kMmaKeys, k_end = last;
+  if (span_tiles > 0) {
+    k_begin = max(k_begin, span * span_tiles * kMmaKeys);
+    k_end = min(k_end, (span + 1) * span_tiles * kMmaKeys - 1);
+  }
+  auto request_tile = [&](int k0, int buf) {
+    __nv_bfloat16* kd = ks_all + buf * kMmaKeys * kst;
+    __nv_bfloat16* vd = vs_all + buf * kMmaKeys * vst;
+    for (int c = tid; c < kMmaKeys * dparts; c += kMmaWarps * 32) {
+      const int kk = c / dparts, part = c - kk * dparts;
+      const int kp = k0 + kk;
+      const bool have = kp <= last && kp >= first;
+      const __nv_bfloat16* src = kcache;
+      if (have) src = kcache + ((static_cast<size_t>(bt[kp / page]) * kv_heads + g) * page + kp % page) * dim + part * 8;
+      bw::copy16_async(bw::smem_addr(kd + kk * kst + part * 8), src, have);
+    }
+    if (vcache) {
+      for (int c = tid; c < kMmaKeys * vparts; c += kMmaWarps * 32) {
+        const int kk = c / vparts, part = c - kk * vparts;
+        const int kp = k0 + kk;
+        const bool have = kp <= last && kp >= first;
+        const __nv_bfloat16* src = vcache;
+        if (have) src = vcache + ((static_cast<size_t>(bt[kp / page]) * kv_heads + g) * page + kp % page) * vdim + part * 8;
+        bw::copy16_async(bw::smem_addr(vd + kk * vst + part * 8), src, have);
+      }
+    }
+    bw::copies_commit();
+  };
+  if (k_begin <= k_end) request_tile(k_begin, 0);
+  for (int k0 = k_begin, buf = 0; k0 <= k_end; k0 += kMmaKeys, buf ^= 1) {
+    // the next tile is requested while this one is used; its buffer was released by the
+    // barrier at the end of the step before
+    if (k0 + kMmaKeys <= k_end) {
+      request_tile(k0 + kMmaKeys, buf ^ 1);
+      bw::copies_wait<1>();
+    } else {
+      bw::copies_wait<0>();
+    }
+    __syncthreads();
+    const __nv_bfloat16* ks = ks_all + buf * kMmaKeys * kst;
+    const __nv_bfloat16* vs = vs_all + buf * kMmaKeys * vst;
+    if (warp_has_rows && k0 <= w_hi && k0 + kMmaKeys > w_lo) {
+    // scores of 16 queries x 32 keys
+    float sc[4][4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.0f;
+    for (int kk = 0; kk < dim; kk += 16) {
+      uint32_t a[4], b[4];
+      bw::ldsm4(a, bw::smem_addr(qs + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * kst + kk + (lane >> 4) * 8));
+#pragma unroll
+      for (int jp = 0; jp < 2; ++jp) {  // 16 keys at a time
+        bw::ldsm4(b, bw::smem_addr(ks + (jp * 16 + (lane >> 4) * 8 + (lane & 7)) * kst + kk + ((lane >> 3) & 1) * 8));
+        bw::mma16816(sc[2 * jp], a, b[0], b[1]);
+        bw::mma16816(sc[2 * jp + 1], a, b[2], b[3]);
+      }
+    }
+    float mt_a = -INFINITY, mt_b = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int kp = k0 + j * 8 + 2 * (lane & 3) + e;
+        float va = modify_score(sc[j][e], sa, slope_a, pq_a, kp);
+        float vb = modify_score(sc[j][2 + e], sa, slope_b, pq_b, kp);
+        if (!(ok_a && kp <= pq_a && kp >= lo_a)) va = -INFINITY;
+        if (!(ok_b && kp <= pq_b && kp >= lo_b)) vb = -INFINITY;
+        sc[j][e] = va, sc[j][2 + e] = vb;
+        mt_a = fmaxf(mt_a, va), mt_b = fmaxf(mt_b, vb);
+      }
+    }
+    mt_a = fmaxf(mt_a, __shfl_xor_sync(0xffffffffu, mt_a, 1)), mt_a = fmaxf(mt_a, __shfl_xor_sync(0xffffffffu, mt_a, 2));
+    mt_b = fmaxf(mt_b, __shfl_xor_sync(0xffffffffu, mt_b, 1)), mt_b = fmaxf(mt_b, __shfl_xor_sync(0xffffffffu, mt_b, 2));
+    const float mn_a = fmaxf(m_a, mt_a), mn_b = fmaxf(m_b, mt_b);
+    const float al_a = m_a == -INFINITY ? 0.0f : expf(__fsub_rn(m_a, mn_a));
+    const float al_b = m_b == -INFINITY ? 0.0f : expf(__fsub_rn(m_b, mn_b));
+    float sum_a = 0.0f, sum_b = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const float pa = sc[j][e] == -INFINITY ? 0.0f : expf(__fsub_rn(sc[j][e], mn_a));
+        const float pb = sc[j][2 + e] == -INFINITY ? 0.0f : expf(__fsub_rn(sc[j][2 + e], mn_b));
+        sc[j][e] = pa, sc[j][2 + e] = pb;
+        sum_a = __fadd_rn(sum_a, pa), sum_b = __fadd_rn(sum_b, pb);
+      }
+    }
+    l_a = __fmaf_rn(l_a, al_a, sum_a), l_b = __fmaf_rn(l_b, al_b, sum_b);  // this thread's share; joined at the end
+    m_a = mn_a, m_b = mn_b;
+#pragma unroll
+    for (int j = 0; j < VT; ++j) {
+      acc[j][0] = __fmul_rn(acc[j][0], al_a), acc[j][1] = __fmul_rn(acc[j][1], al_a);
+      acc[j][2] = __fmul_rn(acc[j][2], al_b), acc[j][3] = __fmul_rn(acc[j][3], al_b);
+    }
+    // weighted values: 16 keys at a time, the weights as hi + lo
+#pragma unroll
+    for (int kb = 0; kb < 2; ++kb) {
+      uint32_t hi[4], lw[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float x0 = sc[2 * kb + (i >> 1)][(i & 1) * 2], x1 = sc[2 * kb + (i >> 1)][(i & 1) * 2 + 1];
+        const __nv_bfloat16 h0b = __float2bfloat16_rn(x0), h1b = __float2bfloat16_rn(x1);
+        hi[i] = bw::pack_bf16(x0, x1);
+        lw[i] = bw::pack_bf16(__fsub_rn(x0, __bfloat162float(h0b)), __fsub_rn(x1, __bfloat162float(h1b)));
+      }
+#pragma unroll
+      for (int jp = 0; jp < VD16; ++jp) {  // 16 value columns at a time
+        uint32_t b[4];
+        bw::ldsm4_trans(b, bw::smem_addr(vs + (kb * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * vst + jp * 16 + (lane >> 4) * 8));
+        bw::mma16816(acc[2 * jp], hi, b[0], b[1]);
+        bw::mma16816(acc[2 * jp], lw, b[0], b[1]);
+        bw::mma16816(acc[2 * jp + 1], hi, b[2], b[3]);
+        bw::mma16816(acc[2 * jp + 1], lw, b[2], b[3]);
+      }
+    }
+    }
+    __syncthreads();  // every warp has used the tile: its buffer may be filled again
+  }
+  bw::copies_wait<0>();  // (a block without a key tile has not waited for its queries' copies yet)
+  l_a = __fadd_rn(l_a, __shfl_xor_sync(0xffffffffu, l_a, 1)), l_a = __fadd_rn(l_a, __shfl_xor_sync(0xffffffffu, l_a, 2));
+  l_b = __fadd_rn(l_b, __shfl_xor_sync(0xffffffffu, l_b, 1)), l_b = __fadd_rn(l_b, __shfl_xor_sync(0xffffffffu, l_b, 2));
+  if (span_tiles > 0) {
+    // the span's record per query: maximum, sum, weighted values relative to that maximum
+    const int colp = 2 * (lane & 3);
+    if (ok_a) {
+      float* rec = partial + ((static_cast<size_t>(row0 + sr_a / nh) * heads + h0 + sr_a % nh) * spans + span) * (vdim + 2);
+      if ((lane & 3) == 0) rec[0] = m_a, rec[1] = l_a;
+#pragma unroll
+      for (int j = 0; j < VT; ++j) rec[2 + j * 8 + colp] = acc[j][0], rec[2 + j * 8 + colp + 1] = acc[j][1];
+    }
+    if (ok_b) {
+      float* rec = partial + ((static_cast<size_t>(row0 + sr_b / nh) * heads + h0 + sr_b % nh) * spans + span) * (vdim + 2);
+      if ((lane & 3) == 0) rec[0] = m_b, rec[1] = l_b;
+#pragma unroll
+      for (int j = 0; j < VT; ++j) rec[2 + j * 8 + colp] = acc[j][2], rec[2 + j * 8 + colp + 1] = acc[j][3];
+    }
+    return;
+  }
+  if (sa.sink) l_a = __fadd_rn(l_a, expf(-m_a)), l_b = __fadd_rn(l_b, expf(-m_b));  // the extra key of score 0
+  const float inv_a = __fdiv_rn(1.0f, l_a), inv_b = __fdiv_rn(1.0f, l_b);
+  const int col = 2 * (lane & 3);
+  if (ok_a) {
+    __nv_bfloat16* dst = out + static_cast<size_t>(row0 + sr_a / nh) * o_stride + (h0 + sr_a % nh) * vdim + col;
+#pragma unroll
+    for (int j = 0; j < VT; ++j)
+      *reinterpret_cast<__nv_bfloat162*>(dst + j * 8) = __floats2bfloat162_rn(__fmul_rn(acc[j][0], inv_a), __fmul_rn(acc[j][1], inv_a));
+  }
+  if (ok_b) {
+    __nv_bfloat16* dst = out + static_cast<size_t>(row0 + sr_b / nh) * o_stride + (h0 + sr_b % nh) * vdim + col;
+#pragma unroll
+    for (int j = 0; j < VT; ++j)
+      *reinterpret_cast<__nv_bfloat162*>(dst + j * 8) = __floats2bfloat162_rn(__fmul_rn(acc[j][2], inv_b), __fmul_rn(acc[j][3], inv_b));
+  }
+}
+
+// The spans' records of a query joined in ascending order of the spans: a warp per query.
+__global__ void __launch_bounds__(128)
+scored_attention_merge_kernel(const float* __restrict__ partial, __nv_bfloat16* out, int o_stride, int queries, int heads,
+                              int vdim, int spans, int sink) {
+  bw::pdl_enter();
+  const int qi = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (qi >= queries) return;
+  const float* rec = partial + static_cast<size_t>(qi) * spans * (vdim + 2);
+  float m = -INFINITY;
+  for (int s = 0; s < spans; ++s) m = fmaxf(m, rec[static_cast<size_t>(s) * (vdim + 2)]);
+  float l = 0.0f;
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+  for (int s = 0; s < spans; ++s) {
+    const float* r = rec + static_cast<size_t>(s) * (vdim + 2);
+    if (r[0] == -INFINITY) continue;  // a span in which the query saw no key
+    const float f = expf(__fsub_rn(r[0], m));
+    l = __fmaf_rn(r[1], f, l);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int d = i * 32 + lane;
+      if (d < vdim) acc[i] = __fmaf_rn(r[2 + d], f, acc[i]);
+    }
+  }
+  if (sink) l = __fadd_rn(l, expf(-m));
+  const float inv = __fdiv_rn(1.0f, l);
+  __nv_bfloat16* dst = out + static_cast<size_t>(qi / heads) * o_stride + (qi % heads) * vdim;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int d = i * 32 + lane;
+    if (d < vdim) dst[d] = __float2bfloat16_rn(__fmul_rn(acc[i], inv));
+  }
+}
+
+template <int VD16>
+int launch_scored_mma(dim3 grid, size_t smem, cudaStream_t stream, const __nv_bfloat16* q, int q_stride,
+                      const __nv_bfloat16* kcache, const __nv_bfloat16* vcache, const int* block_table, int max_blocks,
+                      const int* tile_seq, const int* tile_row0, const int* tile_rows, const int* seq_pos0,
+                      const int* seq_row0, __nv_bfloat16* out, int o_stride, int heads, int kv_heads, int hb, int dim,
+                      int page, const ScoreArgs& sa, int span_tiles, int spans, float* partial) {
+  static size_t allowed = 48 * 1024;
+  if (smem > allowed) {
+    cudaError_t e = cudaFuncSetAttribute(scored_attention_mma_kernel<VD16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(smem));
+    if (e != cudaSuccess) {
+      bw::set_error("scored_attention: %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+      return static_cast<int>(e);
+    }
+    allowed = smem;
+  }
+  bw::launch_pdl(scored_attention_mma_kernel<VD16>, grid, dim3(kMmaWarps * 32), smem, stream, q, q_stride, kcache, vcache,
+                 block_table, max_blocks, tile_seq, tile_row0, tile_rows, seq_pos0, seq_row0, out, o_stride, heads, kv_heads,
+                 hb, dim, page, sa, span_tiles, spans, partial);
+  return bw::launch_status();
+}
+
+bool g_force_plain = false;
+constexpr int kSpanTiles = 8;  // key tiles per span of a step of single rows: 256 keys, whatever the step
+#endif  // BW_ACT_BF16
+
 }  // namespace
 
 // Rows of one sequence per query tile for `group` query heads on a key/value head.
@@ -348,7 +632,8 @@ BW_API int BW_FN(qkv_prepare)(const float* u, int cols, const float* conv_w, int
   a.block_table = block_table, a.max_blocks = max_blocks;
   a.kcache = static_cast<act_t*>(kcache), a.vcache = static_cast<act_t*>(vcache), a.q_out = static_cast<act_t*>(q_out);
   a.heads = heads, a.kv_heads = kv_heads, a.v_heads = vcache ? kv_heads : 0, a.dim = dim, a.vdim = vdim, a.page = page;
-  bw::launch_pdl(qkv_prepare_kernel, dim3(n), dim3(kPrepWarps * 32), 0, stream, a);
+  const int total = heads + kv_heads + a.v_heads;
+  bw::launch_pdl(qkv_prepare_kernel, dim3(n, (total + kPrepWarps - 1) / kPrepWarps), dim3(kPrepWarps * 32), 0, stream, a);
   return bw::launch_status();
 }
 
@@ -403,3 +688,67 @@ BW_API int BW_FN(scored_attention)(const void* q, int q_stride, const void* kcac
 #undef BW_SCORED
   return -1;
 }
+
+#if BW_ACT_BF16
+// Tests: keep attention on the CUDA-core kernel also where the tensor-core kernel takes the shape.
+BW_API int bw_bf16_scored_attention_force_plain(int on) {
+  g_force_plain = on != 0;
+  return 0;
+}
+
+// Rows of one sequence per query tile of the tensor-core kernel, 0 where it does not take the
+// shape: key size a multiple of 16, value size 16 .. 128 in steps of 16, or 256.
+BW_API int bw_bf16_scored_attention_mma_tile_rows(int group, int dim, int vdim) {
+  if (g_force_plain || dim % 16 || vdim % 16 || dim > 256 || !(vdim <= 128 || vdim == 256)) return 0;
+  const int hb = group < kMmaRows ? group : kMmaRows;
+  return kMmaRows / (hb > 0 ? hb : 1);
+}
+
+BW_API int bw_bf16_scored_attention_mma(const void* q, int q_stride, const void* kcache, const void* vcache,
+                                        const int* block_table, int max_blocks, const int* tile_seq, const int* tile_row0,
+                                        const int* tile_rows, int tiles, const int* seq_pos0, const int* seq_row0, void* out,
+                                        int o_stride, int heads, int kv_heads, int dim, int vdim, int page, float scale,
+                                        float softcap, int sink, const float* slopes, int window, int n, int spans,
+                                        float* partial, cudaStream_t stream) {
+  // spans > 1 (a step of single rows, `partial` holding n * heads * spans * (vdim + 2) floats): every
+  // row's keys are spread over blocks of kSpanTiles key tiles each, and a second kernel joins them.
+  if (tiles <= 0) return 0;
+  if (kv_heads <= 0 || heads % kv_heads || !bw_bf16_scored_attention_mma_tile_rows(heads / kv_heads, dim, vdim)) {
+    bw::set_error("scored_attention (tensor cores): %d heads on %d, sizes %d / %d", heads, kv_heads, dim, vdim);
+    return -1;
+  }
+  const int rep = heads / kv_heads;
+  const int hb = rep < kMmaRows ? rep : kMmaRows;
+  const size_t smem = (static_cast<size_t>(kMmaRows + 2 * kMmaKeys) * (dim + 8) +
+                       (vcache ? static_cast<size_t>(2 * kMmaKeys) * (vdim + 8) : 0)) * sizeof(__nv_bfloat16);
+  ScoreArgs sa;
+  sa.scale = scale, sa.softcap = softcap, sa.sink = sink, sa.slopes = slopes, sa.window = window;
+  const bool split = spans > 1 && partial != nullptr;
+  if (!split) spans = 1;
+  const dim3 grid(tiles, kv_heads, (rep + hb - 1) / hb * spans);
+  typedef const __nv_bfloat16* in_t;
+  int rc = -1;
+#define BW_SCORED_MMA(V)                                                                                                   \
+  case V:                                                                                                                  \
+    rc = launch_scored_mma<V>(grid, smem, stream, static_cast<in_t>(q), q_stride, static_cast<in_t>(kcache),               \
+                              static_cast<in_t>(vcache), block_table, max_blocks, tile_seq, tile_row0, tile_rows, seq_pos0, \
+                              seq_row0, static_cast<__nv_bfloat16*>(out), o_stride, heads, kv_heads, hb, dim, page, sa,     \
+                              split ? kSpanTiles : 0, spans, partial);                                                      \
+    break;
+  switch (vdim / 16) {
+    BW_SCORED_MMA(1) BW_SCORED_MMA(2) BW_SCORED_MMA(3) BW_SCORED_MMA(4) BW_SCORED_MMA(5) BW_SCORED_MMA(6) BW_SCORED_MMA(7)
+    BW_SCORED_MMA(8) BW_SCORED_MMA(16)
+  }
+#undef BW_SCORED_MMA
+  if (rc != 0 || !split) return rc;
+  bw::launch_pdl(scored_attention_merge_kernel, dim3((n * heads + 3) / 4), dim3(128), 0, stream,
+                 static_cast<const float*>(partial), static_cast<__nv_bfloat16*>(out), o_stride, n * heads, heads, vdim, spans, sink);
+  return bw::launch_status();
+}
+
+// Spans that a step of single rows with contexts of up to max_keys keys is spread over.
+BW_API int bw_bf16_scored_attention_spans(int max_keys) {
+  const int per = kSpanTiles * kMmaKeys;
+  return (max_keys + per - 1) / per;
+}
+#endif  // BW_ACT_BF16

@@ -931,7 +931,23 @@ class KernelOps:
         """The heights of query tiles (rows of one sequence per thread block) that ``scored_attention``
         wants prepared for ``group`` query heads on a key/value head."""
         fn = getattr(self._mixers_lib(), f"bw_{self.kind}_scored_attention_tile_rows")
-        return [int(fn(_c_int(group)))]
+        out = [int(fn(_c_int(group)))]
+        tc = self._scored_mma_rows(group, dim, vdim)
+        if tc and tc not in out:
+            out.append(tc)
+        return out
+
+    def _scored_mma_rows(self, group: int, dim: int, vdim: int) -> int:
+        """Rows per query tile of the tensor-core attention, 0 where it does not take the shape."""
+        if self.kind != "bf16":
+            return 0
+        return int(self._mixers_lib().bw_bf16_scored_attention_mma_tile_rows(_c_int(group), _c_int(dim), _c_int(vdim)))
+
+    def plain_mixers(self, on: bool) -> None:
+        """Tests: keep scored attention on the CUDA-core kernel (one chain of fused multiply-adds per
+        score and output) also where the tensor-core kernel would take the shape."""
+        if self.kind == "bf16":
+            self._mixers_lib().bw_bf16_scored_attention_force_plain(_c_int(int(on)))
 
     def qkv_prepare(self, u: torch.Tensor, conv_w: Optional[torch.Tensor], conv_state: Optional[torch.Tensor],
                     q_norm: Optional[torch.Tensor], k_norm: Optional[torch.Tensor], eps: float,
@@ -1017,7 +1033,23 @@ class KernelOps:
         if q.shape[1] != heads * dim or tuple(out.shape) != (n, heads * vdim) or kcache.shape[1] != kv_heads or \
                 kcache.shape[3] != dim:
             raise KernelError("scored_attention: shapes do not fit the heads")
-        t_seq, t_row0, t_rows, t_count = batch.query_tiles(self.scored_attention_tile_heights(heads // kv_heads, dim, vdim)[0])
+        tc_rows = self._scored_mma_rows(heads // kv_heads, dim, vdim)
+        if tc_rows and (not hasattr(batch, "tile_sets") or tc_rows in batch.tile_sets):
+            # the serving precision's tensor-core kernel; a step of single rows with long contexts
+            # spreads every row's keys over spans of 256 (whatever the step's size) and merges
+            t_seq, t_row0, t_rows, t_count = batch.query_tiles(tc_rows)
+            spans, scratch, launches = 1, None, 1
+            if t_count == n and batch.max_keys > 256:
+                spans = int(self._mixers_lib().bw_bf16_scored_attention_spans(_c_int(batch.max_keys)))
+                scratch, launches = self._latent_scratch(n * heads * spans * (vdim + 2), q.device), 2
+            self._mcall("scored_attention_mma", _p(q), _c_int(q.shape[1]), _p(kcache), _p(vcache), _p(block_table),
+                        _c_int(block_table.shape[1]), _p(t_seq), _p(t_row0), _p(t_rows), _c_int(t_count), _p(batch.seq_pos0),
+                        _p(batch.seq_row0), _p(out), _c_int(out.shape[1]), _c_int(heads), _c_int(kv_heads), _c_int(dim),
+                        _c_int(vdim), _c_int(kcache.shape[2]), _c_float(scale), _c_float(softcap), _c_int(int(bool(sink))),
+                        _p(slopes), _c_int(window), _c_int(n), _c_int(spans), _p(scratch), self._stream(), launches=launches)
+            return
+        fn = getattr(self._mixers_lib(), f"bw_{self.kind}_scored_attention_tile_rows")
+        t_seq, t_row0, t_rows, t_count = batch.query_tiles(int(fn(_c_int(heads // kv_heads))))
         self._mcall("scored_attention", _p(q), _c_int(q.shape[1]), _p(kcache), _p(vcache), _p(block_table),
                     _c_int(block_table.shape[1]), _p(t_seq), _p(t_row0), _p(t_rows), _c_int(t_count), _p(batch.seq_pos0),
                     _p(batch.seq_row0), _p(out), _c_int(out.shape[1]), _c_int(heads), _c_int(kv_heads), _c_int(dim),
@@ -1026,11 +1058,12 @@ class KernelOps:
 
     def gla_scan(self, u: torch.Tensor, z: torch.Tensor, bias: torch.Tensor, tau: float, state: torch.Tensor,
                  norm_w: torch.Tensor, eps: float, out: torch.Tensor, heads: int, dim: int, vdim: int, q_scale: float,
-                 batch, seq_tiles) -> None:
+                 batch, seq_tiles, scratch: Optional[torch.Tensor] = None) -> None:
         """The recurrence S_t = diag(a_t) S_(t-1) + k_t v_t^T, o_t = S_t^T (q_t * q_scale) per head over the
         rows of every sequence of the step (``seq_tiles``: one tile per sequence), from and into ``state``
         [slots, heads, dim, vdim] (zero at a request's first position), with a = sigmoid(z + bias) ** (1 /
-        tau); out = o / rms(o) * norm_w * silu(gate).  ``u`` (float32) holds q | k | v | gate per row."""
+        tau); out = o / rms(o) * norm_w * silu(gate).  ``u`` (float32) holds q | k | v | gate per row.
+        ``scratch``: float32 [n, heads * vdim] for the outputs before their norm (allocated when absent)."""
         n = u.shape[0]
         _need(u, torch.float32, "gla_scan u", 2)
         _need(z, torch.float32, "gla_scan z", 2)
@@ -1042,9 +1075,15 @@ class KernelOps:
                 tuple(state.shape[1:]) != (heads, dim, vdim) or norm_w.shape[0] != vdim or tuple(out.shape) != (n, heads * vdim):
             raise KernelError("gla_scan: shapes do not fit the heads")
         t_seq, t_row0, t_rows, t_count = seq_tiles
+        if scratch is None:
+            scratch = torch.empty(n, heads * vdim, dtype=torch.float32, device=u.device)
+        _need(scratch, torch.float32, "gla_scan scratch", 2)
+        if tuple(scratch.shape) != (n, heads * vdim):
+            raise KernelError("gla_scan: the scratch is not [rows, heads * vdim]")
         self._mcall("gla_scan", _p(u), _c_int(u.shape[1]), _p(z), _p(bias), _c_float(tau), _p(state), _p(norm_w),
-                    _c_float(eps), _p(out), _p(t_seq), _p(t_row0), _p(t_rows), _c_int(t_count), _p(batch.seq_pos0),
-                    _p(batch.seq_slot), _c_int(heads), _c_int(dim), _c_int(vdim), _c_float(q_scale), self._stream())
+                    _c_float(eps), _p(scratch), _p(out), _p(t_seq), _p(t_row0), _p(t_rows), _c_int(t_count),
+                    _p(batch.seq_pos0), _p(batch.seq_slot), _c_int(n), _c_int(heads), _c_int(dim), _c_int(vdim),
+                    _c_float(q_scale), self._stream(), launches=2)
 
 
 _OPS = {}

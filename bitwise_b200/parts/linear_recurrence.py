@@ -86,8 +86,9 @@ class GatedLinearAttention(Mixer):
         z = ws.rows("gla_decay32", n, self.qk_cols, torch.float32)
         ops.linear(low, self.w_decay_up, z)
         gated = ws.rows("gla_out", n, self.v_cols, ctx.act_dtype)
+        o32 = ws.rows("gla_out32", n, self.v_cols, torch.float32)
         ops.gla_scan(u, z, self.decay_bias, self.tau, cache.state, self.norm, self.eps, gated, self.heads, self.dim,
-                     self.vdim, self.dim ** -0.5, ctx, ctx.query_tiles(SEQUENCE_TILE))
+                     self.vdim, self.dim ** -0.5, ctx, ctx.query_tiles(SEQUENCE_TILE), scratch=o32)
         ops.linear(gated, self.w_o, x, residual=x if accumulate else None)
 
 

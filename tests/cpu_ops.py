@@ -112,7 +112,7 @@ class CpuOps:
             den = e.sum(-1, keepdim=True) + (torch.exp(-m) if sink else 0.0)
             out[r] = torch.einsum("hk,khd->hd", e / den, v).reshape(-1).to(out.dtype)
 
-    def gla_scan(self, u, z, bias, tau, state, norm_w, eps, out, heads, dim, vdim, q_scale, ctx, tiles):
+    def gla_scan(self, u, z, bias, tau, state, norm_w, eps, out, heads, dim, vdim, q_scale, ctx, tiles, scratch=None):
         t_seq, t_row0, t_rows, count = tiles
         hd, hv = heads * dim, heads * vdim
         for i in range(count):

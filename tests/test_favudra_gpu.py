@@ -175,7 +175,9 @@ def fill_pages(seq_tensors, table, page, kv_heads, size, dtype):
     return cache
 
 
-ATTENTION_SHAPES = [(4, 2, 16, 24), (8, 1, 128, 128), (3, 3, 40, 8), (40, 1, 8, 40), (2, 1, 96, 200)]
+# (the serving precision runs shapes with sizes in steps of 16 on the tensor cores, the others on the CUDA cores)
+ATTENTION_SHAPES = [(4, 2, 16, 24), (8, 1, 128, 128), (3, 3, 40, 8), (40, 1, 8, 40), (2, 1, 96, 200), (6, 2, 64, 32),
+                    (80, 1, 16, 16), (2, 2, 32, 256)]
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -192,7 +194,7 @@ def test_capped_sink_attention(dtype, heads, kv_heads, dim, vdim, cap):
     q, k, v = rt(T, heads, dim), rt(T, kv_heads, dim), rt(T, kv_heads, vdim)
     scale = 1.0 / math.sqrt(dim)
     k[5] = (q[690, 0] * 3).to(act(dtype)).to(F64)        # a far key that query 690 of head 0 agrees with
-    q[650] = (-q[650].abs() * 4).to(act(dtype)).to(F64)
+    q[650] = (-q[650].abs() * (40 / math.sqrt(dim))).to(act(dtype)).to(F64)
     k[:651] = k[:651].abs()                              # every score of row 650 is very negative
     k[5] = k[5].abs()
     want = P.capped_sink_attention(q, k, v, scale, cap)
@@ -225,14 +227,14 @@ def test_distance_window_attention(dtype, heads, kv_heads, dim, window):
     W = window or T
     for i, inside in ((200, True), (250, False), (W + 1, False), (280, True)):
         j = i - W + 1 if inside else i - W
-        if j >= 0:
+        if j >= 0 and i < T:
             q[i] = (k[j, 0] * 4).to(act(dtype)).to(F64)
     want = P.distance_window_attention(q, k, scale, window or None)
     # pages that the window has passed are given back in a live engine: their table entries are -1
     table = pages_in_no_order([(0, T)], 30, page, g)
     kc = fill_pages([k], table, page, kv_heads, dim, dtype)
     slopes = torch.tensor(distance_slopes(heads), dtype=torch.float32, device=DEV)
-    for seqs in ([(0, T)], [(190, 70)], [(199, 2)], [(250, 1)], [(280, 1)], [(W + 1, 1)] if W + 1 < T else [(5, 1)]):
+    for seqs in ([(0, T)], [(190, 70)], [(199, 2)], [(250, 1)], [(280, 1)], [(W + 1, 1)] if W + 1 < T else [(5, 1)]):  # noqa: E501
         p0, n = seqs[0]
         b = Batch(seqs)
         tb = table.clone()
@@ -265,6 +267,45 @@ def test_attention_of_unequal_sequences_in_one_step(dtype):
     want = torch.cat([P.capped_sink_attention(qs[s], ks[s], vs[s], 0.2, 9.0)[p0:p0 + n].reshape(n, -1)
                       for s, (p0, n) in enumerate(seqs)])
     close(out, want, dtype, "three sequences", 2.0)
+    # single rows at unequal depths: one below the span of keys from which rows are spread over blocks
+    seqs = [(89, 1), (199, 1), (332, 1)]
+    b = Batch(seqs)
+    qrows = torch.cat([qs[s][p0:p0 + n].reshape(n, -1) for s, (p0, n) in enumerate(seqs)])
+    out = torch.empty(b.n, heads * vdim, dtype=act(dtype), device=DEV)
+    ops.scored_attention(qrows.to(act(dtype)).to(DEV).contiguous(), kc, vc, table, out, heads, kv_heads, dim, vdim, 0.2, 9.0,
+                         True, None, 0, b)
+    want = torch.cat([P.capped_sink_attention(qs[s], ks[s], vs[s], 0.2, 9.0)[p0:p0 + n].reshape(n, -1)
+                      for s, (p0, n) in enumerate(seqs)])
+    close(out, want, dtype, "three single rows", 2.0)
+
+
+def test_tensor_core_attention_agrees_with_the_plain_kernel():
+    """bfloat16: the same step on both kernels (prompt portion, then single rows spread over spans)."""
+    from bitwise_b200.parts.scored_attention import distance_slopes
+    ops = ops_of("bfloat16")
+    heads, kv_heads, dim, vdim, page, T = 8, 2, 64, 64, 16, 600
+    g = torch.Generator().manual_seed(5)
+    k = torch.randn(T, kv_heads, dim, generator=g).to(torch.bfloat16)
+    v = torch.randn(T, kv_heads, vdim, generator=g).to(torch.bfloat16)
+    table = pages_in_no_order([(0, T)], 40, page, g)
+    kc, vc = fill_pages([k], table, page, kv_heads, dim, "bfloat16"), fill_pages([v], table, page, kv_heads, vdim, "bfloat16")
+    slopes = torch.tensor(distance_slopes(heads), dtype=torch.float32, device=DEV)
+    for seqs in ([(100, 500)], [(599, 1)]):
+        b = Batch(seqs)
+        q = torch.randn(b.n, heads * dim, generator=g).to(torch.bfloat16).to(DEV)
+        outs = []
+        for plain in (False, True):
+            ops.plain_mixers(plain)
+            try:
+                o1 = torch.empty(b.n, heads * vdim, dtype=torch.bfloat16, device=DEV)
+                ops.scored_attention(q, kc, vc, table, o1, heads, kv_heads, dim, vdim, 0.125, 12.0, True, None, 0, b)
+                o2 = torch.empty(b.n, heads * dim, dtype=torch.bfloat16, device=DEV)
+                ops.scored_attention(q, kc, None, table, o2, heads, kv_heads, dim, dim, 0.125, 0.0, False, slopes, 100, b)
+            finally:
+                ops.plain_mixers(False)
+            outs.append((o1.float(), o2.float()))
+        for a, c in zip(*outs):
+            assert float((a - c).abs().max()) <= 0.02 * float(c.abs().max())
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
