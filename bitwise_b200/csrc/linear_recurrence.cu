@@ -17,7 +17,7 @@
 
 namespace {
 
-constexpr int kChunk = 16;   // tokens staged at a time
+constexpr int kChunk = 32;   // tokens staged at a time
 constexpr int kCols = 32;    // value columns per block
 constexpr int kMaxParts = 8; // row partitions per block
 
@@ -26,6 +26,9 @@ __device__ __forceinline__ float log_sigmoid(float x) { return __fsub_rn(fminf(x
 
 __device__ __forceinline__ void copy4_async(float* dst, const float* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(dst))), "l"(src));
+}
+__device__ __forceinline__ void copy16_async(float* dst, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(dst))), "l"(src));
 }
 __device__ __forceinline__ void copies_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N>
@@ -53,7 +56,7 @@ struct ScanArgs {
 template <int R, bool VEC /* dim is a multiple of 4: a partition's q, k and decays are read 16 bytes at a time */>
 __global__ void __launch_bounds__(kMaxParts * kCols) gla_scan_kernel(const ScanArgs a) {
   bw::pdl_enter();
-  extern __shared__ float sm[];
+  extern __shared__ __align__(16) float sm[];
   const int dim = a.dim, vdim = a.vdim, P = a.parts;
   const int W = 3 * dim + kCols;                 // a staged token: q | k | z (then the decay) | 32 values
   float* stage = sm;                             // [2][kChunk][W]
@@ -72,8 +75,27 @@ __global__ void __launch_bounds__(kMaxParts * kCols) gla_scan_kernel(const ScanA
     const int row = p * R + i;
     S[i] = (!fresh && col_ok && row < dim) ? sp[static_cast<size_t>(row) * vdim] : 0.0f;
   }
+  // (16 bytes at a time where every row and head starts on 16 bytes)
+  const bool wide = VEC && (vdim & 3) == 0 && (a.stride & 3) == 0 &&
+                    ((reinterpret_cast<uintptr_t>(a.u) | reinterpret_cast<uintptr_t>(a.z)) & 15) == 0;
   auto request = [&](int first, float* buf) {
     const int len = min(kChunk, cnt - first);
+    if (wide) {
+      const int W4 = W >> 2;
+      for (int i = tid; i < len * W4; i += threads) {
+        const int tt = i / W4, e = (i - tt * W4) << 2;
+        const size_t r = static_cast<size_t>(row0 + first + tt);
+        const float* src;
+        if (e < dim) src = a.u + r * a.stride + h * dim + e;
+        else if (e < 2 * dim) src = a.u + r * a.stride + hd + h * dim + (e - dim);
+        else if (e < 3 * dim) src = a.z + r * hd + h * dim + (e - 2 * dim);
+        else if (c0 + e - 3 * dim < vdim) src = a.u + r * a.stride + 2 * hd + h * vdim + c0 + (e - 3 * dim);
+        else continue;
+        copy16_async(buf + tt * W + e, src);
+      }
+      copies_commit();
+      return;
+    }
     for (int i = tid; i < len * W; i += threads) {
       const int tt = i / W, e = i - tt * W;
       const size_t r = static_cast<size_t>(row0 + first + tt);
