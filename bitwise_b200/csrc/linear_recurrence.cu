@@ -3,7 +3,7 @@
 // followed by the root-mean-square norm of o_t over vdim (times a weight) and the gate silu(g_t).
 //
 // The columns of S do not meet before the norm, so a block walks the rows of one sequence of the
-// step for one head and 32 value columns, token by token, from the state that the request's slot
+// step for one head and 8 value columns, token by token, from the state that the request's slot
 // holds (zero at a request's first position). Thread (p, j) keeps rows p R .. p R + R - 1 of
 // column j in registers. The tokens' q, k, z and v are copied into shared memory a chunk ahead
 // (cp.async, two buffers), the decays are formed there, and the partial outputs of the row
@@ -17,12 +17,20 @@
 
 namespace {
 
-constexpr int kChunk = 32;   // tokens staged at a time
-constexpr int kCols = 32;    // value columns per block
-constexpr int kMaxParts = 8; // row partitions per block
+constexpr int kCols = 8;      // value columns per block: a head's columns are spread over many blocks
+constexpr int kMaxThreads = 256;
 
-// log(sigmoid(x)) without overflow: min(x, 0) - log1p(exp(-|x|)).
-__device__ __forceinline__ float log_sigmoid(float x) { return __fsub_rn(fminf(x, 0.0f), log1pf(expf(-fabsf(x)))); }
+// log(sigmoid(x)) without overflow: min(x, 0) - log1p(exp(-|x|)). The serving precision takes the
+// hardware's exponential and logarithm (relative error about 1e-7, far below a bfloat16 operand's).
+__device__ __forceinline__ float decay_of(float x, float inv_tau) {
+#if BW_ACT_BF16
+  const float ls = __fsub_rn(fminf(x, 0.0f), __logf(__fadd_rn(1.0f, __expf(-fabsf(x)))));
+  return __expf(__fmul_rn(ls, inv_tau));
+#else
+  const float ls = __fsub_rn(fminf(x, 0.0f), log1pf(expf(-fabsf(x))));
+  return expf(__fmul_rn(ls, inv_tau));
+#endif
+}
 
 __device__ __forceinline__ void copy4_async(float* dst, const float* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(dst))), "l"(src));
@@ -49,18 +57,19 @@ struct ScanArgs {
   const int* tile_rows;
   const int* seq_pos0;
   const int* seq_slot;
-  int heads, dim, vdim, parts;
+  int heads, dim, vdim, parts, chunk;
   float q_scale;
 };
 
-template <int R, bool VEC /* dim is a multiple of 4: a partition's q, k and decays are read 16 bytes at a time */>
-__global__ void __launch_bounds__(kMaxParts * kCols) gla_scan_kernel(const ScanArgs a) {
+// Thread (p, j): rows p R .. p R + R - 1 of column c0 + j of S. R is 2, 4, 8 or 16.
+template <int R, bool VEC /* dim is a multiple of 4: a thread's q, k and decays are read as vectors */>
+__global__ void __launch_bounds__(kMaxThreads) gla_scan_kernel(const ScanArgs a) {
   bw::pdl_enter();
   extern __shared__ __align__(16) float sm[];
-  const int dim = a.dim, vdim = a.vdim, P = a.parts;
-  const int W = 3 * dim + kCols;                 // a staged token: q | k | z (then the decay) | 32 values
-  float* stage = sm;                             // [2][kChunk][W]
-  float* part = sm + 2 * kChunk * W;             // [kChunk][P][kCols]
+  const int dim = a.dim, vdim = a.vdim, P = a.parts, chunk = a.chunk;
+  const int W = 3 * dim + kCols;                 // a staged token: q | k | z (then the decay) | 8 values
+  float* stage = sm;                             // [2][chunk][W]
+  float* part = sm + 2 * chunk * W;              // [chunk][P][kCols]
   const int t = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * kCols;
   const int seq = a.tile_seq[t], row0 = a.tile_row0[t], cnt = a.tile_rows[t];
   const int tid = threadIdx.x, threads = blockDim.x;
@@ -73,31 +82,17 @@ __global__ void __launch_bounds__(kMaxParts * kCols) gla_scan_kernel(const ScanA
 #pragma unroll
   for (int i = 0; i < R; ++i) {
     const int row = p * R + i;
-    S[i] = (!fresh && col_ok && row < dim) ? sp[static_cast<size_t>(row) * vdim] : 0.0f;
+    S[i] = (!fresh && col_ok && p < P && row < dim) ? sp[static_cast<size_t>(row) * vdim] : 0.0f;
   }
   // (16 bytes at a time where every row and head starts on 16 bytes)
   const bool wide = VEC && (vdim & 3) == 0 && (a.stride & 3) == 0 &&
                     ((reinterpret_cast<uintptr_t>(a.u) | reinterpret_cast<uintptr_t>(a.z)) & 15) == 0;
   auto request = [&](int first, float* buf) {
-    const int len = min(kChunk, cnt - first);
-    if (wide) {
-      const int W4 = W >> 2;
-      for (int i = tid; i < len * W4; i += threads) {
-        const int tt = i / W4, e = (i - tt * W4) << 2;
-        const size_t r = static_cast<size_t>(row0 + first + tt);
-        const float* src;
-        if (e < dim) src = a.u + r * a.stride + h * dim + e;
-        else if (e < 2 * dim) src = a.u + r * a.stride + hd + h * dim + (e - dim);
-        else if (e < 3 * dim) src = a.z + r * hd + h * dim + (e - 2 * dim);
-        else if (c0 + e - 3 * dim < vdim) src = a.u + r * a.stride + 2 * hd + h * vdim + c0 + (e - 3 * dim);
-        else continue;
-        copy16_async(buf + tt * W + e, src);
-      }
-      copies_commit();
-      return;
-    }
-    for (int i = tid; i < len * W; i += threads) {
-      const int tt = i / W, e = i - tt * W;
+    const int len = min(chunk, cnt - first);
+    const int step = wide ? 4 : 1;
+    const int Ws = W / step;
+    for (int i = tid; i < len * Ws; i += threads) {
+      const int tt = i / Ws, e = (i - tt * Ws) * step;
       const size_t r = static_cast<size_t>(row0 + first + tt);
       const float* src;
       if (e < dim) src = a.u + r * a.stride + h * dim + e;
@@ -105,17 +100,18 @@ __global__ void __launch_bounds__(kMaxParts * kCols) gla_scan_kernel(const ScanA
       else if (e < 3 * dim) src = a.z + r * hd + h * dim + (e - 2 * dim);
       else if (c0 + e - 3 * dim < vdim) src = a.u + r * a.stride + 2 * hd + h * vdim + c0 + (e - 3 * dim);
       else continue;
-      copy4_async(buf + i, src);
+      if (wide) copy16_async(buf + tt * W + e, src);
+      else copy4_async(buf + tt * W + e, src);
     }
     copies_commit();
   };
   request(0, stage);
-  for (int first = 0, b = 0; first < cnt; first += kChunk, b ^= 1) {
-    const int len = min(kChunk, cnt - first);
-    float* buf = stage + b * kChunk * W;
+  for (int first = 0, b = 0; first < cnt; first += chunk, b ^= 1) {
+    const int len = min(chunk, cnt - first);
+    float* buf = stage + b * chunk * W;
     __syncthreads();  // the other buffer and `part` have been used
-    if (first + kChunk < cnt) {
-      request(first + kChunk, stage + (b ^ 1) * kChunk * W);
+    if (first + chunk < cnt) {
+      request(first + chunk, stage + (b ^ 1) * chunk * W);
       copies_wait<1>();
     } else {
       copies_wait<0>();
@@ -125,7 +121,7 @@ __global__ void __launch_bounds__(kMaxParts * kCols) gla_scan_kernel(const ScanA
       const int tt = i / dim, d = i - tt * dim;
       float* tok = buf + tt * W;
       tok[d] = __fmul_rn(tok[d], a.q_scale);
-      tok[2 * dim + d] = expf(__fmul_rn(log_sigmoid(__fadd_rn(tok[2 * dim + d], a.bias[h * dim + d])), a.inv_tau));
+      tok[2 * dim + d] = decay_of(__fadd_rn(tok[2 * dim + d], a.bias[h * dim + d]), a.inv_tau);
     }
     __syncthreads();
     if (p < P) {
@@ -136,26 +132,33 @@ __global__ void __launch_bounds__(kMaxParts * kCols) gla_scan_kernel(const ScanA
         const float* qt = tok + p * R;
         const float* kt = tok + dim + p * R;
         const float* at = tok + 2 * dim + p * R;
-        float o = 0.0f;
-        if (VEC) {
+        float qv[R], kv[R], av[R];
+        if (VEC && R >= 4) {
 #pragma unroll
           for (int i = 0; i < R; i += 4) {
-            if (p * R + i < dim) {
-              const float4 q4 = *reinterpret_cast<const float4*>(qt + i), k4 = *reinterpret_cast<const float4*>(kt + i),
-                           a4 = *reinterpret_cast<const float4*>(at + i);
-              S[i] = __fmaf_rn(a4.x, S[i], __fmul_rn(k4.x, v)), o = __fmaf_rn(q4.x, S[i], o);
-              S[i + 1] = __fmaf_rn(a4.y, S[i + 1], __fmul_rn(k4.y, v)), o = __fmaf_rn(q4.y, S[i + 1], o);
-              S[i + 2] = __fmaf_rn(a4.z, S[i + 2], __fmul_rn(k4.z, v)), o = __fmaf_rn(q4.z, S[i + 2], o);
-              S[i + 3] = __fmaf_rn(a4.w, S[i + 3], __fmul_rn(k4.w, v)), o = __fmaf_rn(q4.w, S[i + 3], o);
-            }
+            const float4 q4 = *reinterpret_cast<const float4*>(qt + i), k4 = *reinterpret_cast<const float4*>(kt + i),
+                         a4 = *reinterpret_cast<const float4*>(at + i);
+            qv[i] = q4.x, qv[i + 1] = q4.y, qv[i + 2] = q4.z, qv[i + 3] = q4.w;
+            kv[i] = k4.x, kv[i + 1] = k4.y, kv[i + 2] = k4.z, kv[i + 3] = k4.w;
+            av[i] = a4.x, av[i + 1] = a4.y, av[i + 2] = a4.z, av[i + 3] = a4.w;
           }
+        } else if (VEC && R == 2) {
+          const float2 q2 = *reinterpret_cast<const float2*>(qt), k2 = *reinterpret_cast<const float2*>(kt),
+                       a2 = *reinterpret_cast<const float2*>(at);
+          qv[0] = q2.x, qv[1] = q2.y, kv[0] = k2.x, kv[1] = k2.y, av[0] = a2.x, av[1] = a2.y;
         } else {
 #pragma unroll
           for (int i = 0; i < R; ++i) {
-            if (p * R + i < dim) {
-              S[i] = __fmaf_rn(at[i], S[i], __fmul_rn(kt[i], v));
-              o = __fmaf_rn(qt[i], S[i], o);
-            }
+            const bool in = p * R + i < dim;
+            qv[i] = in ? qt[i] : 0.0f, kv[i] = in ? kt[i] : 0.0f, av[i] = in ? at[i] : 0.0f;
+          }
+        }
+        float o = 0.0f;
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+          if (VEC || p * R + i < dim) {  // (with VEC, R divides dim: every row of a partition exists)
+            S[i] = __fmaf_rn(av[i], S[i], __fmul_rn(kv[i], v));
+            o = __fmaf_rn(qv[i], S[i], o);
           }
         }
         part[(tt * P + p) * kCols + j] = o;
@@ -218,8 +221,8 @@ int launch_scan_v(const ScanArgs& a, int tiles, int threads, size_t smem, cudaSt
 template <int R>
 int launch_scan(const ScanArgs& a, int tiles, int threads, size_t smem, cudaStream_t stream) {
   // (the order of a column's operations is the same either way: the same bits)
-  return a.dim % 4 == 0 ? launch_scan_v<R, true>(a, tiles, threads, smem, stream)
-                        : launch_scan_v<R, false>(a, tiles, threads, smem, stream);
+  return a.dim % 4 == 0 && a.dim % R == 0 ? launch_scan_v<R, true>(a, tiles, threads, smem, stream)
+                                          : launch_scan_v<R, false>(a, tiles, threads, smem, stream);
 }
 
 }  // namespace
@@ -230,30 +233,36 @@ BW_API int BW_FN(gla_scan)(const float* u, int stride, const float* z, const flo
                            const int* tile_rows, int tiles, const int* seq_pos0, const int* seq_slot, int n, int heads,
                            int dim, int vdim, float q_scale, cudaStream_t stream) {
   if (tiles <= 0 || n <= 0) return 0;
-  // state rows per thread: the fewest of 8, 16, 32, 64 with which eight partitions cover the head
-  int rows = 8;
-  while (rows < 64 && (dim + rows - 1) / rows > kMaxParts) rows *= 2;
+  // state rows per thread: the fewest of 2, 4, 8, 16 with which a block stays within 256 threads
+  int rows = 2;
+  while (rows < 16 && (dim + rows - 1) / rows * kCols > kMaxThreads) rows *= 2;
   ScanArgs a;
   a.u = u, a.stride = stride, a.z = z, a.bias = bias, a.inv_tau = 1.0f / tau, a.state = state, a.o = o32;
   a.tile_seq = tile_seq, a.tile_row0 = tile_row0, a.tile_rows = tile_rows;
   a.seq_pos0 = seq_pos0, a.seq_slot = seq_slot, a.heads = heads, a.dim = dim, a.vdim = vdim, a.q_scale = q_scale;
   a.parts = (dim + rows - 1) / rows;
-  if (a.parts > kMaxParts) {
-    bw::set_error("gla_scan: key size %d (up to %d)", dim, 64 * kMaxParts);
+  if (a.parts * kCols > kMaxThreads) {
+    bw::set_error("gla_scan: key size %d (up to %d)", dim, 16 * kMaxThreads / kCols);
     return -1;
   }
-  const int threads = a.parts * kCols;
-  const size_t smem = (static_cast<size_t>(2 * kChunk) * (3 * dim + kCols) + static_cast<size_t>(kChunk) * a.parts * kCols) * sizeof(float);
-  if (smem > 200 * 1024) {
-    bw::set_error("gla_scan: key size %d needs %zu bytes of shared memory", dim, smem);
-    return -1;
-  }
+  const int threads = (a.parts * kCols + 31) / 32 * 32;
+  // Tokens staged at a time: no more than the longest sequence of the step can have (a step of
+  // single rows stages one, so that many of its small blocks share an SM), and as many of 32 as
+  // let two blocks share an SM's shared memory.
+  int longest = n - tiles + 1;
+  a.chunk = 1;
+  while (a.chunk < 32 && a.chunk < longest) a.chunk *= 2;
+  auto bytes = [&](int chunk) {
+    return (static_cast<size_t>(2 * chunk) * (3 * dim + kCols) + static_cast<size_t>(chunk) * a.parts * kCols) * sizeof(float);
+  };
+  while (a.chunk > 4 && bytes(a.chunk) > 100 * 1024) a.chunk /= 2;
+  const size_t smem = bytes(a.chunk);
   int rc = -1;
   switch (rows) {
+    case 2: rc = launch_scan<2>(a, tiles, threads, smem, stream); break;
+    case 4: rc = launch_scan<4>(a, tiles, threads, smem, stream); break;
     case 8: rc = launch_scan<8>(a, tiles, threads, smem, stream); break;
     case 16: rc = launch_scan<16>(a, tiles, threads, smem, stream); break;
-    case 32: rc = launch_scan<32>(a, tiles, threads, smem, stream); break;
-    case 64: rc = launch_scan<64>(a, tiles, threads, smem, stream); break;
   }
   if (rc != 0) return rc;
   bw::launch_pdl(gla_finish_kernel, dim3(n), dim3(128), 0, stream, static_cast<const float*>(o32), u, stride,
