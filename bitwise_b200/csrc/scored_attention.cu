@@ -625,7 +625,7 @@ int launch_scored_mma(dim3 grid, size_t smem, cudaStream_t stream, const __nv_bf
 }
 
 bool g_force_plain = false;
-constexpr int kSpanTiles = 8;  // key tiles per span of a step of single rows: 256 keys, whatever the step
+constexpr int kSpanTiles = 4;  // key tiles per span of a step of single rows: 128 keys, whatever the step's size
 #endif  // BW_ACT_BF16
 
 }  // namespace

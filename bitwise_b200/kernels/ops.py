@@ -1036,7 +1036,7 @@ class KernelOps:
         tc_rows = self._scored_mma_rows(heads // kv_heads, dim, vdim)
         if tc_rows and (not hasattr(batch, "tile_sets") or tc_rows in batch.tile_sets):
             # the serving precision's tensor-core kernel; a step of single rows with long contexts
-            # spreads every row's keys over spans of 256 (whatever the step's size) and merges
+            # spreads every row's keys over spans of 128 (whatever the step's size) and merges
             t_seq, t_row0, t_rows, t_count = batch.query_tiles(tc_rows)
             spans, scratch, launches = 1, None, 1
             if t_count == n and batch.max_keys > 256:
