@@ -627,7 +627,8 @@ def favudra_kernel_table(z, pk, page=16):
         cw = torch.randn(cols, taps, device=dev)
         st = torch.zeros(nseq + 1, taps - 1, cols, device=dev)
         nw = torch.ones(hd, device=dev)
-        ms = timed_device(lambda: (ops.qkv_prepare(u, cw, st, nw, nw, 1e-5, cos, sin, b, table, kc, vc, q, H, G, hd, hd),
+        cwt = cw.t().contiguous()
+        ms = timed_device(lambda: (ops.qkv_prepare(u, cw, st, nw, nw, 1e-5, cos, sin, b, table, kc, vc, q, H, G, hd, hd, conv_wt=cwt),
                             ops.conv_state_update(u, st, b, taps, b.query_tiles(SEQUENCE_TILE))), flush=flush)
         tms = timed_device(lambda: ops.rope_cache(qkv, b.pos, b.row_seq, cos_t, sin_t, table, kc, vc, H, G, hd), flush=flush)
         put(f"conv_norm_rotate_store_{label}", ms, frac_bytes(n * cols * 6, ms), tms, frac_bytes(n * cols * 4, tms), "copy bandwidth")

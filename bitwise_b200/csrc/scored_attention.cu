@@ -31,6 +31,7 @@ struct PrepArgs {
   const float* u;            // [n, cols] projected rows: q heads, then k heads, then v heads
   int cols;
   const float* conv_w;       // [cols, taps] or null
+  const float* conv_wt;      // the same transposed, [taps, cols], for the kernel that reads four channels at a time
   int taps;
   const float* conv_state;   // [slots, taps - 1, cols] or null
   const float* q_norm;       // [dim] or null
@@ -138,6 +139,115 @@ __global__ void __launch_bounds__(kPrepWarps * 32) qkv_prepare_kernel(const Prep
   }
 }
 
+// The same with four consecutive entries of a head per lane (head sizes and column counts that are
+// multiples of 4): the projected rows, the state, the taps (transposed: [taps, cols]) and the norm
+// weights are read 16 bytes at a time, a rotation's partners lie in one lane, and a lane stores its
+// four results at once. Lane l holds entries 4 l .. 4 l + 3 and 128 + 4 l .. of the head.
+#if BW_ACT_BF16
+__device__ __forceinline__ void store4(__nv_bfloat16* dst, float4 v) {
+  uint2 w;
+  w.x = bw::pack_bf16(v.x, v.y), w.y = bw::pack_bf16(v.z, v.w);
+  *reinterpret_cast<uint2*>(dst) = w;
+}
+#else
+__device__ __forceinline__ void store4(float* dst, float4 v) { *reinterpret_cast<float4*>(dst) = v; }
+#endif
+
+__global__ void __launch_bounds__(kPrepWarps * 32) qkv_prepare_vec_kernel(const PrepArgs a) {
+  bw::pdl_enter();
+  const int r = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int p = a.pos[r];
+  const int seq = a.row_seq[r];
+  const int row0 = a.seq_row0[seq];
+  const int slot = a.conv_state ? a.seq_slot[seq] : 0;
+  const int total = a.heads + a.kv_heads + a.v_heads;
+  const float* urow = a.u + static_cast<size_t>(r) * a.cols;
+  for (int hs = blockIdx.y * kPrepWarps + warp; hs < total; hs += kPrepWarps * gridDim.y) {
+    int size, col0;
+    const float* norm_w;
+    bool turns;
+    if (hs < a.heads + a.kv_heads) {
+      size = a.dim, col0 = hs * a.dim, norm_w = hs < a.heads ? a.q_norm : a.k_norm, turns = true;
+    } else {
+      size = a.vdim, col0 = (a.heads + a.kv_heads) * a.dim + (hs - a.heads - a.kv_heads) * a.vdim, norm_w = nullptr;
+      turns = false;
+    }
+    float4 val[2];
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int e0 = 4 * lane + 128 * j;
+      float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      if (e0 < size) {
+        const int c = col0 + e0;
+        if (a.conv_wt) {
+          for (int t = 0; t < a.taps; ++t) {  // taps ascending, as in the kernel above
+            const int back = a.taps - 1 - t;
+            if (p - back < 0) continue;
+            const int rr = r - back;
+            const float* src = rr >= row0 ? urow - static_cast<size_t>(back) * a.cols + c
+                                          : a.conv_state + (static_cast<size_t>(slot) * (a.taps - 1) + (a.taps - 1 - (row0 - rr))) * a.cols + c;
+            const float4 x = *reinterpret_cast<const float4*>(src);
+            const float4 w = *reinterpret_cast<const float4*>(a.conv_wt + static_cast<size_t>(t) * a.cols + c);
+            v.x = __fmaf_rn(w.x, x.x, v.x), v.y = __fmaf_rn(w.y, x.y, v.y), v.z = __fmaf_rn(w.z, x.z, v.z), v.w = __fmaf_rn(w.w, x.w, v.w);
+          }
+        } else {
+          v = *reinterpret_cast<const float4*>(urow + c);
+        }
+        ss = __fmaf_rn(v.x, v.x, ss), ss = __fmaf_rn(v.y, v.y, ss), ss = __fmaf_rn(v.z, v.z, ss), ss = __fmaf_rn(v.w, v.w, ss);
+      }
+      val[j] = v;
+    }
+    if (norm_w) {
+      const float inv = bw::rms_scale(bw::warp_sum(ss), size, a.eps);
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int e0 = 4 * lane + 128 * j;
+        if (e0 < size) {
+          const float4 w = *reinterpret_cast<const float4*>(norm_w + e0);
+          val[j].x = bw::rms_apply(val[j].x, inv, w.x), val[j].y = bw::rms_apply(val[j].y, inv, w.y);
+          val[j].z = bw::rms_apply(val[j].z, inv, w.z), val[j].w = bw::rms_apply(val[j].w, inv, w.w);
+        }
+      }
+    }
+    if (turns && a.pairs > 0) {
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int e0 = 4 * lane + 128 * j;
+        if (e0 >= size) continue;
+        const int i0 = e0 >> 1;
+        const size_t at = static_cast<size_t>(p) * a.pairs;
+        if (i0 < a.pairs) {
+          const float c = a.cos_t[at + i0], s = a.sin_t[at + i0];
+          const float x = val[j].x, y = val[j].y;
+          val[j].x = __fsub_rn(__fmul_rn(x, c), __fmul_rn(y, s)), val[j].y = __fadd_rn(__fmul_rn(y, c), __fmul_rn(x, s));
+        }
+        if (i0 + 1 < a.pairs) {
+          const float c = a.cos_t[at + i0 + 1], s = a.sin_t[at + i0 + 1];
+          const float x = val[j].z, y = val[j].w;
+          val[j].z = __fsub_rn(__fmul_rn(x, c), __fmul_rn(y, s)), val[j].w = __fadd_rn(__fmul_rn(y, c), __fmul_rn(x, s));
+        }
+      }
+    }
+    act_t* dst;
+    if (hs < a.heads) {
+      dst = a.q_out + static_cast<size_t>(r) * a.heads * a.dim + hs * a.dim;
+    } else {
+      const int blk = a.block_table[static_cast<size_t>(seq) * a.max_blocks + p / a.page];
+      if (hs < a.heads + a.kv_heads)
+        dst = a.kcache + ((static_cast<size_t>(blk) * a.kv_heads + (hs - a.heads)) * a.page + p % a.page) * a.dim;
+      else
+        dst = a.vcache + ((static_cast<size_t>(blk) * a.v_heads + (hs - a.heads - a.kv_heads)) * a.page + p % a.page) * a.vdim;
+    }
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int e0 = 4 * lane + 128 * j;
+      if (e0 < size) store4(dst + e0, val[j]);
+    }
+  }
+}
+
 // state[slot][i] = the projected row of position end - (taps - 1) + i (i < taps - 1), `end` the
 // request's length after this step: from the step's rows, from the old state, or zero before
 // position 0. One thread per (sequence, channel) reads all it needs before it writes.
@@ -190,6 +300,7 @@ struct ScoreArgs {
   int window;
 };
 
+#if BW_ACT_BF16
 // The same on the serving precision's tensor-core path, where the scores come from bfloat16
 // operands: tanh through the hardware's exponential, tanh(x) = 1 - 2 / (exp(2x) + 1) (relative
 // error of a few 1e-7, against the 4e-3 of a bfloat16 operand).
@@ -202,6 +313,7 @@ __device__ __forceinline__ float modify_score_fast(float s, const ScoreArgs& sa,
   if (sa.slopes) s = __fsub_rn(s, __fmul_rn(slope, static_cast<float>(pq - kp)));
   return s;
 }
+#endif
 
 __device__ __forceinline__ float modify_score(float s, const ScoreArgs& sa, float slope, int pq, int kp) {
   s = __fmul_rn(s, sa.scale);
@@ -636,7 +748,8 @@ BW_API int BW_FN(scored_attention_tile_rows)(int group) {
   return (kWarps * kQW) / (hb > 0 ? hb : 1);
 }
 
-BW_API int BW_FN(qkv_prepare)(const float* u, int cols, const float* conv_w, int taps, const float* conv_state,
+BW_API int BW_FN(qkv_prepare)(const float* u, int cols, const float* conv_w, const float* conv_wt, int taps,
+                              const float* conv_state,
                               const float* q_norm, const float* k_norm, float eps, const float* cos_t, const float* sin_t,
                               int pairs, const int* pos, const int* row_seq, const int* seq_row0, const int* seq_pos0,
                               const int* seq_slot, const int* block_table, int max_blocks, void* kcache, void* vcache,
@@ -652,14 +765,23 @@ BW_API int BW_FN(qkv_prepare)(const float* u, int cols, const float* conv_w, int
     return -1;
   }
   PrepArgs a;
-  a.u = u, a.cols = cols, a.conv_w = conv_w, a.taps = taps, a.conv_state = taps > 1 ? conv_state : nullptr;
+  a.u = u, a.cols = cols, a.conv_w = conv_w, a.conv_wt = conv_w ? conv_wt : nullptr, a.taps = taps;
+  a.conv_state = taps > 1 ? conv_state : nullptr;
   a.q_norm = q_norm, a.k_norm = k_norm, a.eps = eps, a.cos_t = cos_t, a.sin_t = sin_t, a.pairs = cos_t ? pairs : 0;
   a.pos = pos, a.row_seq = row_seq, a.seq_row0 = seq_row0, a.seq_pos0 = seq_pos0, a.seq_slot = seq_slot;
   a.block_table = block_table, a.max_blocks = max_blocks;
   a.kcache = static_cast<act_t*>(kcache), a.vcache = static_cast<act_t*>(vcache), a.q_out = static_cast<act_t*>(q_out);
   a.heads = heads, a.kv_heads = kv_heads, a.v_heads = vcache ? kv_heads : 0, a.dim = dim, a.vdim = vdim, a.page = page;
   const int total = heads + kv_heads + a.v_heads;
-  bw::launch_pdl(qkv_prepare_kernel, dim3(n, (total + kPrepWarps - 1) / kPrepWarps), dim3(kPrepWarps * 32), 0, stream, a);
+  // four entries per lane where every head and row starts on 16 bytes (and the taps came transposed)
+  const bool by_four = dim % 4 == 0 && vdim % 4 == 0 && cols % 4 == 0 && (!conv_w || conv_wt) &&
+                       ((reinterpret_cast<uintptr_t>(u) | reinterpret_cast<uintptr_t>(conv_state) |
+                         reinterpret_cast<uintptr_t>(conv_wt) | reinterpret_cast<uintptr_t>(q_norm) |
+                         reinterpret_cast<uintptr_t>(k_norm)) & 15) == 0;
+  if (by_four)
+    bw::launch_pdl(qkv_prepare_vec_kernel, dim3(n, (total + kPrepWarps - 1) / kPrepWarps), dim3(kPrepWarps * 32), 0, stream, a);
+  else
+    bw::launch_pdl(qkv_prepare_kernel, dim3(n, (total + kPrepWarps - 1) / kPrepWarps), dim3(kPrepWarps * 32), 0, stream, a);
   return bw::launch_status();
 }
 

@@ -953,14 +953,16 @@ class KernelOps:
                     q_norm: Optional[torch.Tensor], k_norm: Optional[torch.Tensor], eps: float,
                     cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], batch, block_table: torch.Tensor,
                     kcache: torch.Tensor, vcache: Optional[torch.Tensor], q_out: torch.Tensor, heads: int,
-                    write_kv_heads: int, dim: int, vdim: int) -> None:
+                    write_kv_heads: int, dim: int, vdim: int, conv_wt: Optional[torch.Tensor] = None) -> None:
         """From the projected rows ``u`` (float32 [n, cols]: ``heads`` query heads of ``dim``, then, when
         ``write_kv_heads`` > 0, that many key heads of ``dim`` and, with ``vcache``, value heads of
         ``vdim``): the convolution over time with ``conv_w`` [cols, taps] (inputs before the step's
         first row of a sequence from ``conv_state`` [slots, taps - 1, cols], zeros before position 0),
         the norm per head of q and k with ``q_norm`` / ``k_norm`` [dim], the rotation of the first 2 *
         pairs entries of q and k by the tables' row of the position; q into ``q_out`` [n, heads * dim],
-        keys and values into their pages.  Each step may be absent (None)."""
+        keys and values into their pages.  Each step may be absent (None).  ``conv_wt``: the taps
+        transposed ([taps, cols]); with them, and sizes that are multiples of 4, the kernel reads four
+        channels at a time."""
         n, cols = u.shape
         _need(u, torch.float32, "qkv_prepare u", 2)
         _need(q_out, self.act_dtype, "qkv_prepare q_out", 2)
@@ -991,7 +993,11 @@ class KernelOps:
             _need(vcache, self.act_dtype, "qkv_prepare vcache", 4)
             if write_kv_heads and tuple(vcache.shape[1:]) != (write_kv_heads, kcache.shape[2], vdim):
                 raise KernelError("qkv_prepare: value cache is not [pages, kv_heads, page, vdim]")
-        self._mcall("qkv_prepare", _p(u), _c_int(cols), _p(conv_w), _c_int(taps), _p(conv_state), _p(q_norm), _p(k_norm),
+        if conv_wt is not None:
+            _need(conv_wt, torch.float32, "qkv_prepare conv_wt", 2)
+            if conv_w is None or tuple(conv_wt.shape) != (taps, cols):
+                raise KernelError("qkv_prepare: the transposed taps are not [taps, cols]")
+        self._mcall("qkv_prepare", _p(u), _c_int(cols), _p(conv_w), _p(conv_wt), _c_int(taps), _p(conv_state), _p(q_norm), _p(k_norm),
                     _c_float(eps), _p(cos), _p(sin), _c_int(pairs), _p(batch.pos), _p(batch.row_seq), _p(batch.seq_row0),
                     _p(batch.seq_pos0), _p(batch.seq_slot), _p(block_table), _c_int(block_table.shape[1]), _p(kcache),
                     _p(vcache if write_kv_heads else None), _p(q_out), _c_int(n), _c_int(heads), _c_int(write_kv_heads),

@@ -70,7 +70,7 @@ class ScoredAttention(Mixer):
         self.k_cols = 0 if shares_cache else kv_heads * dim
         self.v_cols = 0 if shares_cache or values_are_keys else kv_heads * vdim
         self.cols = self.q_cols + self.k_cols + self.v_cols
-        self.w_in = self.w_o = self.conv_w = self.q_norm = self.k_norm = self.slopes = None
+        self.w_in = self.w_o = self.conv_w = self.conv_wt = self.q_norm = self.k_norm = self.slopes = None
 
     # -- what the cache keeps --------------------------------------------------------------
     def cache_need(self):
@@ -119,6 +119,7 @@ class ScoredAttention(Mixer):
         self.w_in = torch.cat(ws, 0).contiguous() if len(ws) > 1 else ws[0]
         if self.taps:
             self.conv_w = torch.cat([state[f"{prefix}.{name}{n['conv']}"] for name, _, _, _ in proj], 0).contiguous()
+            self.conv_wt = self.conv_w.t().contiguous()  # [taps, channels]: four channels of a tap lie together
         if self.qk_norm:
             self.q_norm = state[f"{prefix}.{n['q']}{n['norm']}"]
             self.k_norm = None if self.shares_cache else state[f"{prefix}.{n['k']}{n['norm']}"]
@@ -127,7 +128,7 @@ class ScoredAttention(Mixer):
             self.slopes = torch.tensor(self.slopes_host, dtype=torch.float32, device=self.w_o.device)
 
     def param_bytes(self) -> int:
-        ts = (self.w_in, self.w_o, self.conv_w, self.q_norm, self.k_norm)
+        ts = (self.w_in, self.w_o, self.conv_w, self.q_norm, self.k_norm)  # (the transposed taps are a copy)
         return sum(t.numel() * t.element_size() for t in ts if t is not None)
 
     # -- one step --------------------------------------------------------------------------
@@ -144,7 +145,7 @@ class ScoredAttention(Mixer):
         writes = cache.writable and not self.shares_cache
         ops.qkv_prepare(u, self.conv_w, state.state if state is not None else None, self.q_norm, self.k_norm, self.eps,
                         cos, sin, ctx, cache.block_table, cache.k, cache.v, q, self.heads,
-                        self.kv_heads if writes else 0, self.dim, self.vdim)
+                        self.kv_heads if writes else 0, self.dim, self.vdim, conv_wt=self.conv_wt)
         if state is not None:
             ops.conv_state_update(u, state.state, ctx, self.taps, ctx.query_tiles(SEQUENCE_TILE))
         mixed = ws.rows("scored_mixed", n, self.heads * self.vdim, ctx.act_dtype)

@@ -31,7 +31,7 @@ class CpuOps:
         return [max(1, 32 // group)]
 
     def qkv_prepare(self, u, conv_w, conv_state, q_norm, k_norm, eps, cos, sin, ctx, block_table, kcache, vcache, q_out,
-                    heads, write_kv_heads, dim, vdim):
+                    heads, write_kv_heads, dim, vdim, conv_wt=None):
         n, cols = u.shape
         page = kcache.shape[2]
         y = u.clone()

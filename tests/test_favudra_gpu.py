@@ -115,7 +115,8 @@ def conv_reference(u, w, heads, kv_heads, dim, vdim, qn, kn, eps, rot):
 @pytest.mark.parametrize("heads,kv_heads,dim,vdim,taps,rot", [(4, 2, 16, 24, 3, (8, 10000.0)), (2, 2, 36, 12, 5, (36, 500.0)),
                                                             (6, 1, 20, 20, 2, (4, 77.0)), (3, 1, 72, 40, 4, None),
                                                             (5, 5, 8, 8, 0, (8, 1e6)), (1, 1, 256, 256, 1, (64, 1e4))])
-def test_convolution_norm_rotation_and_state_across_steps(dtype, heads, kv_heads, dim, vdim, taps, rot):
+@pytest.mark.parametrize("by_four", [False, True])
+def test_convolution_norm_rotation_and_state_across_steps(dtype, heads, kv_heads, dim, vdim, taps, rot, by_four):
     """One sequence fed in portions (single rows, pairs, portions shorter and longer than the taps)
     beside another sequence that starts late in a slot someone else left dirty."""
     from bitwise_b200.parts.rope import RotaryEncoding
@@ -149,8 +150,10 @@ def test_convolution_norm_rotation_and_state_across_steps(dtype, heads, kv_heads
         b = Batch(seqs, slots=[2 - s for s in who])
         u = torch.cat(rows).to(DEV)
         q = torch.empty(b.n, heads * dim, dtype=act(dtype), device=DEV)
+        # (with the taps transposed as well, shapes in steps of 4 take the kernel that reads four channels at a time)
         ops.qkv_prepare(u, w.to(DEV) if taps else None, state, qn.to(DEV), kn.to(DEV), 1e-5, cos, sin, b,
-                        table[who].contiguous(), kc, vc, q, heads, kv_heads, dim, vdim)
+                        table[who].contiguous(), kc, vc, q, heads, kv_heads, dim, vdim,
+                        conv_wt=w.t().contiguous().to(DEV) if taps and by_four else None)
         if taps > 1:
             ops.conv_state_update(u, state, b, taps, b.query_tiles(SEQ))
         r = 0
