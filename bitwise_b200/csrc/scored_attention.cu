@@ -294,6 +294,7 @@ constexpr int kThreads = kWarps * 32;
 constexpr int kQW = 4;  // queries per warp
 
 struct ScoreArgs {
+  float cap_exp;  // 2 * scale / softcap * log2(e): the exponent of the cap's exponential per unit of raw score
   float scale, softcap;
   int sink;
   const float* slopes;  // [heads] or null
@@ -305,10 +306,12 @@ struct ScoreArgs {
 // operands: tanh through the hardware's exponential, tanh(x) = 1 - 2 / (exp(2x) + 1) (relative
 // error of a few 1e-7, against the 4e-3 of a bfloat16 operand).
 __device__ __forceinline__ float modify_score_fast(float s, const ScoreArgs& sa, float slope, int pq, int kp) {
-  s = __fmul_rn(s, sa.scale);
   if (sa.softcap > 0.0f) {
-    const float e = __expf(__fmul_rn(2.0f, __fdividef(s, sa.softcap)));
-    s = __fmul_rn(sa.softcap, __fsub_rn(1.0f, __fdividef(2.0f, __fadd_rn(e, 1.0f))));
+    // cap * tanh(x) = cap - 2 cap / (exp(2x) + 1), x = s * scale / cap; exp(2x) = 2^(s * cap_exp)
+    const float e = bw::exp2_approx(__fmul_rn(s, sa.cap_exp));
+    s = __fmaf_rn(__fmul_rn(-2.0f, sa.softcap), __fdividef(1.0f, __fadd_rn(e, 1.0f)), sa.softcap);
+  } else {
+    s = __fmul_rn(s, sa.scale);
   }
   if (sa.slopes) s = __fsub_rn(s, __fmul_rn(slope, static_cast<float>(pq - kp)));
   return s;
@@ -485,13 +488,6 @@ scored_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, c
   const int p0 = seq_pos0[seq] + (row0 - seq_row0[seq]);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int dparts = dim >> 3, vparts = vdim >> 3;
-  for (int c = tid; c < kMmaRows * dparts; c += kMmaWarps * 32) {
-    const int sr = c / dparts, part = c - sr * dparts;
-    const bool valid = sr < nq;
-    const __nv_bfloat16* src = valid ? q + static_cast<size_t>(row0 + sr / nh) * q_stride + (h0 + sr % nh) * dim + part * 8 : q;
-    bw::copy16_async(bw::smem_addr(qs + sr * kst + part * 8), src, valid);
-  }
-  bw::copies_commit();
   // this thread's two queries: stacked rows sa_ and sb_ of the block
   const int sr_a = warp * 16 + (lane >> 2), sr_b = sr_a + 8;
   const bool ok_a = sr_a < nq, ok_b = sr_b < nq;
@@ -503,6 +499,9 @@ scored_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, c
   const int w_first = min(warp * 16, max(nq - 1, 0)) / nh, w_last = min(warp * 16 + 15, max(nq - 1, 0)) / nh;
   const int w_lo = sa.window > 0 ? max(0, p0 + w_first - sa.window + 1) : 0, w_hi = p0 + w_last;
   const bool warp_has_rows = warp * 16 < nq;
+  const bool warp_full = warp * 16 + 15 < nq;  // all 16 stacked rows of the warp are queries
+  const int w_seen_to = p0 + w_first;           // keys up to here are seen by every query of the warp ...
+  const int w_seen_from = sa.window > 0 ? max(0, p0 + w_last - sa.window + 1) : 0;  // ... from here on
   float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.0f, l_b = 0.0f;
   float acc[VT][4];
 #pragma unroll
@@ -516,7 +515,23 @@ scored_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, c
   if (span_tiles > 0) {
     k_begin = max(k_begin, span * span_tiles * kMmaKeys);
     k_end = min(k_end, (span + 1) * span_tiles * kMmaKeys - 1);
+    if (k_begin > k_end) {
+      // none of the block's queries reaches into this span: records that say so, nothing else
+      for (int sr = tid; sr < nq; sr += kMmaWarps * 32) {
+        float* rec = partial + ((static_cast<size_t>(row0 + sr / nh) * heads + h0 + sr % nh) * spans + span) * (vdim + 2);
+        rec[0] = -INFINITY, rec[1] = 0.0f;
+      }
+      return;
+    }
   }
+  // the queries' rows (a block with keys to walk only)
+  for (int c = tid; c < kMmaRows * dparts; c += kMmaWarps * 32) {
+    const int sr = c / dparts, part = c - sr * dparts;
+    const bool valid = sr < nq;
+    const __nv_bfloat16* src = valid ? q + static_cast<size_t>(row0 + sr / nh) * q_stride + (h0 + sr % nh) * dim + part * 8 : q;
+    bw::copy16_async(bw::smem_addr(qs + sr * kst + part * 8), src, valid);
+  }
+  bw::copies_commit();
   // The threads are laid over a tile's 16-byte parts as (key, part) with the parts rounded up to a
   // power of two, so that every thread keeps its part and steps through the keys.
   int pk = 1, pv = 1;
@@ -582,17 +597,33 @@ scored_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, c
       }
     }
     float mt_a = -INFINITY, mt_b = -INFINITY;
+    // a tile that every query of the warp sees whole needs no mask
+    const bool whole = warp_full && k0 + kMmaKeys - 1 <= w_seen_to && k0 >= w_seen_from;
+    if (whole) {
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+      for (int j = 0; j < 4; ++j) {
 #pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int kp = k0 + j * 8 + 2 * (lane & 3) + e;
-        float va = modify_score_fast(sc[j][e], sa, slope_a, pq_a, kp);
-        float vb = modify_score_fast(sc[j][2 + e], sa, slope_b, pq_b, kp);
-        if (!(ok_a && kp <= pq_a && kp >= lo_a)) va = -INFINITY;
-        if (!(ok_b && kp <= pq_b && kp >= lo_b)) vb = -INFINITY;
-        sc[j][e] = va, sc[j][2 + e] = vb;
-        mt_a = fmaxf(mt_a, va), mt_b = fmaxf(mt_b, vb);
+        for (int e = 0; e < 2; ++e) {
+          const int kp = k0 + j * 8 + 2 * (lane & 3) + e;
+          const float va = modify_score_fast(sc[j][e], sa, slope_a, pq_a, kp);
+          const float vb = modify_score_fast(sc[j][2 + e], sa, slope_b, pq_b, kp);
+          sc[j][e] = va, sc[j][2 + e] = vb;
+          mt_a = fmaxf(mt_a, va), mt_b = fmaxf(mt_b, vb);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int kp = k0 + j * 8 + 2 * (lane & 3) + e;
+          float va = modify_score_fast(sc[j][e], sa, slope_a, pq_a, kp);
+          float vb = modify_score_fast(sc[j][2 + e], sa, slope_b, pq_b, kp);
+          if (!(ok_a && kp <= pq_a && kp >= lo_a)) va = -INFINITY;
+          if (!(ok_b && kp <= pq_b && kp >= lo_b)) vb = -INFINITY;
+          sc[j][e] = va, sc[j][2 + e] = vb;
+          mt_a = fmaxf(mt_a, va), mt_b = fmaxf(mt_b, vb);
+        }
       }
     }
     mt_a = fmaxf(mt_a, __shfl_xor_sync(0xffffffffu, mt_a, 1)), mt_a = fmaxf(mt_a, __shfl_xor_sync(0xffffffffu, mt_a, 2));
@@ -613,10 +644,13 @@ scored_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, c
     }
     l_a = __fmaf_rn(l_a, al_a, sum_a), l_b = __fmaf_rn(l_b, al_b, sum_b);  // this thread's share; joined at the end
     m_a = mn_a, m_b = mn_b;
+    // (a maximum that stayed gives the factor exp(0) = 1 exactly: nothing to rescale then)
+    if (__any_sync(0xffffffffu, al_a != 1.0f || al_b != 1.0f)) {
 #pragma unroll
-    for (int j = 0; j < VT; ++j) {
-      acc[j][0] = __fmul_rn(acc[j][0], al_a), acc[j][1] = __fmul_rn(acc[j][1], al_a);
-      acc[j][2] = __fmul_rn(acc[j][2], al_b), acc[j][3] = __fmul_rn(acc[j][3], al_b);
+      for (int j = 0; j < VT; ++j) {
+        acc[j][0] = __fmul_rn(acc[j][0], al_a), acc[j][1] = __fmul_rn(acc[j][1], al_a);
+        acc[j][2] = __fmul_rn(acc[j][2], al_b), acc[j][3] = __fmul_rn(acc[j][3], al_b);
+      }
     }
     // weighted values: 16 keys at a time, the weights as hi + lo
 #pragma unroll
@@ -737,7 +771,7 @@ int launch_scored_mma(dim3 grid, size_t smem, cudaStream_t stream, const __nv_bf
 }
 
 bool g_force_plain = false;
-constexpr int kSpanTiles = 4;  // key tiles per span of a step of single rows: 128 keys, whatever the step's size
+constexpr int kSpanTiles = 8;  // key tiles per span: 256 keys, whatever the step
 #endif  // BW_ACT_BF16
 
 }  // namespace
@@ -823,6 +857,7 @@ BW_API int BW_FN(scored_attention)(const void* q, int q_stride, const void* kcac
   }
   ScoreArgs sa;
   sa.scale = scale, sa.softcap = softcap, sa.sink = sink, sa.slopes = slopes, sa.window = window;
+  sa.cap_exp = 0.0f;  // (the tensor-core kernel's)
   const dim3 grid(tiles, kv_heads, (rep + hb - 1) / hb);
 #define BW_SCORED(A)                                                                                                      \
   case A:                                                                                                                 \
@@ -858,8 +893,9 @@ BW_API int bw_bf16_scored_attention_mma(const void* q, int q_stride, const void*
                                         int o_stride, int heads, int kv_heads, int dim, int vdim, int page, float scale,
                                         float softcap, int sink, const float* slopes, int window, int n, int spans,
                                         float* partial, cudaStream_t stream) {
-  // spans > 1 (a step of single rows, `partial` holding n * heads * spans * (vdim + 2) floats): every
-  // row's keys are spread over blocks of kSpanTiles key tiles each, and a second kernel joins them.
+  // spans > 1 (`partial` holding n * heads * spans * (vdim + 2) floats): every query's keys are spread
+  // over blocks of kSpanTiles key tiles each, at fixed absolute positions, and a second kernel joins
+  // the spans' records in ascending order.
   if (tiles <= 0) return 0;
   if (kv_heads <= 0 || heads % kv_heads || !bw_bf16_scored_attention_mma_tile_rows(heads / kv_heads, dim, vdim)) {
     bw::set_error("scored_attention (tensor cores): %d heads on %d, sizes %d / %d", heads, kv_heads, dim, vdim);
@@ -871,6 +907,7 @@ BW_API int bw_bf16_scored_attention_mma(const void* q, int q_stride, const void*
                        (vcache ? static_cast<size_t>(2 * kMmaKeys) * (vdim + 8) : 0)) * sizeof(__nv_bfloat16);
   ScoreArgs sa;
   sa.scale = scale, sa.softcap = softcap, sa.sink = sink, sa.slopes = slopes, sa.window = window;
+  sa.cap_exp = softcap > 0.0f ? 2.0f * scale / softcap * 1.4426950408889634f : 0.0f;
   const bool split = spans > 1 && partial != nullptr;
   if (!split) spans = 1;
   const dim3 grid(tiles, kv_heads, (rep + hb - 1) / hb * spans);

@@ -1041,11 +1041,14 @@ class KernelOps:
             raise KernelError("scored_attention: shapes do not fit the heads")
         tc_rows = self._scored_mma_rows(heads // kv_heads, dim, vdim)
         if tc_rows and (not hasattr(batch, "tile_sets") or tc_rows in batch.tile_sets):
-            # the serving precision's tensor-core kernel; a step of single rows with long contexts
-            # spreads every row's keys over spans of 128 (whatever the step's size) and merges
+            # The serving precision's tensor-core kernel.  Contexts beyond 256 keys are walked in spans
+            # of 256 keys at fixed absolute positions, a block per query tile and span, and a second
+            # kernel joins the spans' records: prompt portions and single rows alike, so that a
+            # position's bits depend neither on the step's kind nor on what else is in it (a query
+            # whose keys lie in the first span gets the same bits with and without the merge).
             t_seq, t_row0, t_rows, t_count = batch.query_tiles(tc_rows)
             spans, scratch, launches = 1, None, 1
-            if t_count == n and batch.max_keys > 256:
+            if batch.max_keys > 256:
                 spans = int(self._mixers_lib().bw_bf16_scored_attention_spans(_c_int(batch.max_keys)))
                 scratch, launches = self._latent_scratch(n * heads * spans * (vdim + 2), q.device), 2
             self._mcall("scored_attention_mma", _p(q), _c_int(q.shape[1]), _p(kcache), _p(vcache), _p(block_table),

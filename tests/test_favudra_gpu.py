@@ -524,3 +524,66 @@ def test_simulated_traces_reproduce_requests_run_alone(dtype):
     out = run_traces(model_of("a", dtype), traces=8, seed=5)
     assert out.traces == 8 and out.requests_checked > 10
     assert out.violations == 0, (out.token_mismatch, out.fingerprint_mismatch, out.hangs, out.leaks)
+
+
+def test_command_line_random_folder_replay_and_generation(tmp_path):
+    """``bitwise_b200 random`` writes a Favudra folder from a config.json; ``bin/trace_run`` replays a mixed
+    schedule on it and ``bitwise_b200 generate`` decodes greedily: both as a user calls them, both
+    against the plain implementation on the folder's own tensors (the decay's inner size is read from
+    the stored shapes)."""
+    import json
+    import os
+    import subprocess
+    import sys
+    from bitwise_b200.weights.safetensors_io import SafetensorsFile
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = CONFIGS["b"]
+    (tmp_path / "config.json").write_text(json.dumps(cfg.to_json()))
+    folder = tmp_path / "model"
+    run = lambda *a, **k: subprocess.run([sys.executable, *a], capture_output=True, text=True, timeout=900, **k)
+    p = run(os.path.join(root, "bin", "bitwise_b200"), "random", "--config", str(tmp_path / "config.json"), "--seed", "11",
+            "--out", str(folder), "--dtype", "bfloat16", "--norm-jitter", "0.2")
+    assert p.returncode == 0, p.stderr[-2000:]
+    f = SafetensorsFile(str(folder / "model.safetensors"))
+    W = {n: f.tensor(n).clone() for n in f.names()}
+    raw = json.load(open(folder / "config.json"))
+    reqs = {f"q{i}": tokens(cfg, n, 300 + i) for i, n in enumerate([33, 70, 2, 19])}
+    steps = R.mixed(reqs, 192, seed=8)
+    out = tmp_path / "out"
+    p = run(os.path.join(root, "bin", "trace_run"), "--model", str(folder), "--dtype", "float32", "--out", str(out),
+            "--max-tokens", "192", input="".join(json.dumps(s) + "\n" for s in steps))
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert [l for l in p.stdout.split("\n") if l.startswith("done")] == [f"done {s['step']}" for s in steps]
+    outs = {s["step"]: np.fromfile(out / f"{s['step']}.f32", dtype="<f4").reshape(-1, cfg.vocab) for s in steps}
+    got = R.collect(steps, outs, cfg.vocab)
+    for rid, toks in reqs.items():
+        want = P.forward(raw, W, toks).numpy()
+        assert np.abs(got[rid] - want).max() <= 1e-4 * np.abs(want).max(), rid
+    prompt = reqs["q3"]
+    p = run(os.path.join(root, "bin", "bitwise_b200"), "generate", "--model", str(folder), "--dtype", "float32",
+            "--max-new-tokens", "6", "--ignore-eos", "--temperature", "0", "--prompt-ids", ",".join(map(str, prompt)))
+    assert p.returncode == 0, p.stderr[-2000:]
+    seq = list(prompt)
+    for t in json.loads(p.stdout.strip().split("\n")[0])["tokens"]:
+        row = P.forward(raw, W, seq)[-1].numpy()
+        assert t == int(row.argmax()) or row.max() - row[t] < 1e-4 * np.abs(row).max()
+        seq.append(t)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["a", "b"])
+def test_cuts_agree_bit_for_bit(name, dtype):
+    """Every kernel of the design walks keys, tokens and products in an order given by its own sizes
+    (key tiles and spans at fixed absolute positions, the recurrence token by token), so the logits of
+    a position are the same bits whole, token by token, in portions and in a crowd: also beyond the
+    256 keys from which a context is walked in spans."""
+    model = model_of(name, dtype)
+    reqs = requests_of(name)
+    vocab = CONFIGS[name].vocab
+    base = R.collect(R.whole(reqs), R.run_in_process(model, R.whole(reqs), 384), vocab)
+    for pname, (steps, pool) in {"tail": (R.tail_one_by_one(reqs, tail=40), 384), "portions": (R.portions(reqs), 384),
+                                 "mixed": (R.mixed(reqs, 704, seed=3), 704)}.items():
+        got = R.collect(steps, R.run_in_process(model, steps, pool), vocab)
+        for rid in reqs:
+            same = (got[rid].view(np.uint32) == base[rid].view(np.uint32)).all(axis=1)
+            assert same.all(), f"{name} {dtype} {pname} {rid}: first position that differs {int(np.argmin(same))}"
