@@ -58,6 +58,20 @@ CONFIGS = {
         layer(window_attention(8, 4, 32, 0.2, window=33), 64))),
 }
 
+# Layer combinations at the edges of what the cache manager sees: no pages at all, no state at all, two
+# windows (two page groups beside the group of full contexts), a one-tap convolution (a factor per
+# channel, no state) whose keys a layer with more query heads and a three-tap convolution reads.
+EDGE_CONFIGS = {
+    "only_gla": FavudraConfig(vocab=50, width=32, eps=1e-5, embedding_scale=2.0, logit_scale=1.0, layers=(
+        layer(gla(2, 8, 8, 3.0, 4), 24), layer(gla(1, 16, 8, 5.0, 2)))),
+    "only_attention": FavudraConfig(vocab=50, width=32, eps=1e-5, embedding_scale=2.0, logit_scale=1.0, layers=(
+        layer(attention(2, 1, 16, 16, 0.3), 24), layer(attention(2, 1, 16, 16, 0.3, kv_from=0)))),
+    "two_windows": FavudraConfig(vocab=50, width=32, eps=1e-5, embedding_scale=2.0, logit_scale=1.0, layers=(
+        layer(window_attention(2, 1, 16, 0.3, window=5), 24), layer(window_attention(4, 4, 8, 0.3, window=40)),
+        layer(attention(2, 2, 16, 8, 0.3, conv=1, rot=(2, 10.0), softcap=2.0), 16),
+        layer(attention(4, 2, 16, 8, 0.3, conv=3, rot=(2, 10.0), kv_from=2)))),
+}
+
 
 def random_weights(config, seed):
     """name -> bfloat16 CPU tensor."""

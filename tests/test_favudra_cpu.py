@@ -11,7 +11,7 @@ import torch
 import plain_favudra as P
 import replay_patterns as R
 from cpu_ops import CpuOps
-from favudra_configs import CONFIGS, random_weights, tokens
+from favudra_configs import CONFIGS, EDGE_CONFIGS, random_weights, tokens
 from bitwise_b200 import Model
 from bitwise_b200.cache.manager import groups_from_needs
 from bitwise_b200.config import ConfigError, FavudraConfig, architecture_of
@@ -120,9 +120,9 @@ def test_plain_convolution_and_recurrence():
 
 
 # -- the engine's host side on the stand-in kernels ---------------------------------------------
-@pytest.mark.parametrize("name", ["a", "b"])
+@pytest.mark.parametrize("name", ["a", "b"] + sorted(EDGE_CONFIGS))
 def test_every_cut_on_the_stand_in(name):
-    cfg = CONFIGS[name]
+    cfg = CONFIGS[name] if name in CONFIGS else EDGE_CONFIGS[name]
     W = random_weights(cfg, 3)
     model = Model.from_tensors(cfg, W, dtype="float32", device="cpu", ops=CpuOps("float32"))
     reqs = {f"{name}{i}": tokens(cfg, n, i) for i, n in enumerate([37, 70, 5, 1, 18])}

@@ -16,7 +16,7 @@ import torch
 
 import plain_favudra as P
 import replay_patterns as R
-from favudra_configs import CONFIGS, random_weights, tokens
+from favudra_configs import CONFIGS, EDGE_CONFIGS, random_weights, tokens
 
 pytestmark = pytest.mark.gpu
 
@@ -449,6 +449,21 @@ def test_every_cut_gives_the_same_logits(name, dtype):
             # between two cuts only rounding differs: far less than between precision and plain
             errs = np.concatenate([row_errors(got[rid], base[rid]) for rid in reqs])
             assert errs.max() <= (1e-5 if dtype == "float32" else 0.02), f"{name} {dtype} {pname}: cuts differ by {errs.max():.3g}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", sorted(EDGE_CONFIGS))
+def test_layer_combinations_at_the_edges(name, dtype):
+    """Models without any pages, without any state, with two windows and a shared one-tap layer."""
+    from bitwise_b200 import Model
+    cfg = EDGE_CONFIGS[name]
+    W = random_weights(cfg, 3)
+    model = Model.from_tensors(cfg, W, dtype=dtype, device=DEV)
+    reqs = {f"{name}{i}": tokens(cfg, n, i) for i, n in enumerate([37, 70, 5, 1, 18])}
+    want = {rid: P.forward(cfg.to_json(), W, t).numpy() for rid, t in reqs.items()}
+    for steps, pool in ((R.whole(reqs), 128), (R.portions(reqs, sizes=(3, 2, 11, 1)), 128), (R.mixed(reqs, 192, seed=5), 192)):
+        got = R.collect(steps, R.run_in_process(model, steps, pool), cfg.vocab)
+        assess([row_errors(got[rid], want[rid]) for rid in reqs], dtype, f"{name} {dtype}")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
