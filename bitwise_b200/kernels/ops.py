@@ -917,15 +917,27 @@ class KernelOps:
             raise KernelError(f"{name} failed ({rc}): " + lib.bw_last_error().decode("utf-8", "replace"))
         self.launches += launches
 
-    def rmsnorm_residual(self, d: torch.Tensor, weight: torch.Tensor, eps: float, x: torch.Tensor) -> None:
-        """x[r] += d[r] / sqrt(mean(d[r]^2) + eps) * weight; d, weight and x float32."""
+    def rmsnorm_residual(self, d: torch.Tensor, weight: torch.Tensor, eps: float, x: torch.Tensor,
+                         next_weight: Optional[torch.Tensor] = None, next_eps: float = 0.0,
+                         next_out: Optional[torch.Tensor] = None) -> None:
+        """x[r] += d[r] / sqrt(mean(d[r]^2) + eps) * weight; d, weight and x float32.  With ``next_weight``
+        and ``next_out`` (act_dtype) also next_out[r] = x[r] / sqrt(mean(x[r]^2) + next_eps) * next_weight of
+        the summed row: the norm before the next sublayer, in the same kernel."""
         n, width = x.shape
         _need(d, torch.float32, "rmsnorm_residual d", 2)
         _need(x, torch.float32, "rmsnorm_residual x", 2)
         _need(weight, torch.float32, "rmsnorm_residual weight", 1)
         if tuple(d.shape) != (n, width) or weight.shape[0] != width:
             raise KernelError("rmsnorm_residual: shapes differ")
-        self._mcall("rmsnorm_residual", _p(d), _p(weight), _p(x), _c_int(n), _c_int(width), _c_float(eps), self._stream())
+        if (next_weight is None) != (next_out is None):
+            raise KernelError("rmsnorm_residual: the next norm needs a weight and an output")
+        if next_out is not None:
+            _need(next_weight, torch.float32, "rmsnorm_residual next_weight", 1)
+            _need(next_out, self.act_dtype, "rmsnorm_residual next_out", 2)
+            if tuple(next_out.shape) != (n, width) or next_weight.shape[0] != width:
+                raise KernelError("rmsnorm_residual: the next norm's shapes differ")
+        self._mcall("rmsnorm_residual", _p(d), _p(weight), _p(x), _c_int(n), _c_int(width), _c_float(eps), _p(next_weight),
+                    _c_float(next_eps), _p(next_out), self._stream())
 
     def scored_attention_tile_heights(self, group: int, dim: int, vdim: int):
         """The heights of query tiles (rows of one sequence per thread block) that ``scored_attention``

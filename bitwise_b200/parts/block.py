@@ -118,9 +118,14 @@ class SandwichBlock(PreNormBlock):
         out = ctx.workspace.rows("sublayer_out", ctx.n, self.width, torch.float32)
         self.mixer_norm.forward(ctx, x, xn)
         self.mixer.forward(ctx, xn, out, cache, accumulate=False)
-        self.mixer_post.forward_residual(ctx, out, x)
         if self.feed_forward is None:
+            self.mixer_post.forward_residual(ctx, out, x)
             return
-        self.ffn_norm.forward(ctx, x, xn)
+        fused = getattr(self.mixer_post, "forward_residual_then", None)
+        if fused is not None:  # the norm after the mixer and the one before the feed-forward in one kernel
+            fused(ctx, out, x, self.ffn_norm, xn)
+        else:
+            self.mixer_post.forward_residual(ctx, out, x)
+            self.ffn_norm.forward(ctx, x, xn)
         self.feed_forward.forward(ctx, xn, out, accumulate=False)
         self.ffn_post.forward_residual(ctx, out, x)

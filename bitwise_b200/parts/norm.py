@@ -47,6 +47,15 @@ class RMSNorm(Norm):
         """x += norm(d): the norm of a sublayer's output ``d`` (float32) on its way into the stream."""
         ctx.ops.rmsnorm_residual(d, self.weight, self.eps, x)
 
+    def forward_residual_then(self, ctx: StepContext, d, x, nxt: "RMSNorm", out) -> None:
+        """``forward_residual(d, x)`` followed by ``nxt.forward(x, out)``, in one kernel where ``nxt`` is a
+        norm of this kind."""
+        if type(nxt) is not RMSNorm or nxt.width != self.width:
+            self.forward_residual(ctx, d, x)
+            nxt.forward(ctx, x, out)
+            return
+        ctx.ops.rmsnorm_residual(d, self.weight, self.eps, x, next_weight=nxt.weight, next_eps=nxt.eps, next_out=out)
+
 
 class LayerNorm(RMSNorm):
     """Mean and variance over the row; a weight, no bias.  ``out`` may be float32 (also ``x``

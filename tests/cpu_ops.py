@@ -23,8 +23,10 @@ class CpuOps:
     def embed_rows(self, table, tokens, out, scale=1.0):
         out.copy_(table[tokens.long()].float() * scale)
 
-    def rmsnorm_residual(self, d, weight, eps, x):
+    def rmsnorm_residual(self, d, weight, eps, x, next_weight=None, next_eps=0.0, next_out=None):
         x += (d * torch.rsqrt(d.pow(2).mean(-1, keepdim=True) + eps)) * weight
+        if next_out is not None:
+            self.rmsnorm(x, next_weight, next_eps, next_out)
 
     # -- scored attention and the linear recurrence (stand-ins shaped like the kernels' interface) --
     def scored_attention_tile_heights(self, group, dim, vdim):

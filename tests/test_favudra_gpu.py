@@ -90,6 +90,12 @@ def test_norm_after_a_sublayer_and_scaled_embedding(dtype, width):
     got = x.clone()
     ops.rmsnorm_residual(d, w + 1.0, 1e-5, got)      # the part folds the offset into the weight when it loads it
     close(got, want, "float32", "x + norm(d)")
+    # ... and the norm before the next sublayer from the same kernel
+    w2 = (0.3 * torch.randn(width, generator=g)).to(DEV)
+    got2, nxt = x.clone(), torch.empty(6, width, dtype=act(dtype), device=DEV)
+    ops.rmsnorm_residual(d, w + 1.0, 1e-5, got2, next_weight=w2 + 1.0, next_eps=1e-5, next_out=nxt)
+    assert torch.equal(got2, got)
+    close(nxt, P.norm_offset(want, w2.cpu().to(F64), 1e-5), dtype, "norm(x + norm(d))")
     table = torch.randn(11, width, generator=g).to(act(dtype)).to(DEV)
     toks = torch.tensor([3, 0, 10, 3], dtype=torch.int32, device=DEV)
     out = torch.empty(4, width, device=DEV)
